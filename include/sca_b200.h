@@ -1,0 +1,208 @@
+/*
+ * sca_b200.h - C ABI of the sm_100a attention kernels (libsca_b200.so).
+ *
+ * This is the seam between the C++ host layer (sca:: public API, dispatcher, KV cache) and the
+ * hand-written CUDA. Every entry point replaces one launch function of the reference and keeps
+ * its argument meaning; the reference interface each one stands in for is cited beside it
+ * (paths relative to the reference repository).
+ *
+ * Conventions
+ *   - plain pointers and sizes only; `stream` is a cudaStream_t passed as void* (NULL = default
+ *     stream); all data pointers are DEVICE pointers unless a comment says "host";
+ *   - return value: 0 on success, otherwise a sci::StatusCode value
+ *     (4 = InvalidArgument, 5 = NotImplemented, 100 = CudaError, 102 = CudaOutOfMemory);
+ *     sca_last_error() returns the message of the last failing call on the calling thread;
+ *   - launches are asynchronous with respect to `stream`; launch errors are checked immediately
+ *     with cudaGetLastError (reference: src/runtime/launcher.cu:94-100);
+ *   - strides are in ELEMENTS, the head dimension is always contiguous (stride 1).
+ *   - there is no CPU fallback: without a CUDA device every launch returns a CudaError code.
+ */
+#ifndef SCA_B200_H_
+#define SCA_B200_H_
+
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#if defined(__GNUC__)
+#define SCA_ABI __attribute__((visibility("default")))
+#else
+#define SCA_ABI
+#endif
+
+/* dtype ids shared by every entry point (reference: decode_splitk.cuh:34 DecodeDtype,
+ * flash_fwd_kernel.cuh:52 dtype_id use the same numbering). */
+enum { SCA_DTYPE_F32 = 0, SCA_DTYPE_F16 = 1, SCA_DTYPE_BF16 = 2 };
+
+/* status codes returned by the entry points (values of sci::StatusCode) */
+enum {
+    SCA_OK = 0,
+    SCA_INVALID_ARGUMENT = 4,
+    SCA_NOT_IMPLEMENTED = 5,
+    SCA_CUDA_ERROR = 100,
+    SCA_CUDA_NOT_AVAILABLE = 101,
+    SCA_CUDA_OOM = 102
+};
+
+/* Message of the most recent failing call on this thread ("" when none). */
+SCA_ABI const char* sca_last_error(void);
+
+/* ------------------------------------------------------------------------------------------ */
+/* device probe - replaces src/runtime/device_probe.h:14-36 (already a C ABI in the reference)  */
+/* ------------------------------------------------------------------------------------------ */
+#define SCA_DEVICE_NAME_MAX 256
+
+typedef struct ScaDeviceProbe {
+    char name[SCA_DEVICE_NAME_MAX];
+    int major;
+    int minor;
+    int sm_count;
+    unsigned long long smem_per_sm;
+    unsigned long long smem_per_block_default;
+    unsigned long long smem_per_block_optin;
+    unsigned long long regs_per_sm;
+    unsigned long long max_threads_per_sm;
+    unsigned long long l2_bytes;
+    unsigned long long total_mem_bytes;
+    unsigned long long free_mem_bytes;
+    int cuda_available;
+    int binary_has_sm80;   /* kept for source compatibility; always 1 (sm_100a is a superset)   */
+    int binary_has_sm90;   /* kept for source compatibility; always 1                           */
+    /* additions for Blackwell (no counterpart in the reference) */
+    int binary_has_sm100a; /* this library carries sm_100a code (tcgen05 / TMEM / TMA)           */
+    int tmem_columns;      /* tensor-memory columns per SM (512 on sm_100), 0 when absent        */
+    int max_cluster_size;  /* portable thread-block-cluster limit                                */
+} ScaDeviceProbe;
+
+/* Fills `out` for `device_id`. 0 on success, non-zero CUDA error code otherwise. */
+SCA_ABI int sca_probe_device(int device_id, ScaDeviceProbe* out);
+/* cudaMemGetInfo wrapper for the current device. 0 on success. */
+SCA_ABI int sca_mem_get_info(unsigned long long* free_bytes, unsigned long long* total_bytes);
+
+/* ------------------------------------------------------------------------------------------ */
+/* flash prefill - replaces sca::cuda::LaunchFlashFwd / FlashFwdParams                          */
+/* (src/backends/flash/flash_fwd_kernel.cuh:32-60, flash_fwd_launch.cu:100-137)                 */
+/* ------------------------------------------------------------------------------------------ */
+typedef struct ScaFlashFwdParams {
+    const void* q;   /* [batch, heads, seq_q, D] through (q_sb, q_sh, q_ss)                      */
+    const void* k;   /* [batch, kv_heads, seq_kv, D] through (k_sb, k_sh, k_ss)                  */
+    const void* v;
+    void* out;       /* same element type as q, through (o_sb, o_sh, o_ss)                       */
+    float* lse;      /* [batch, heads, seq_q] fp32, natural log; may be NULL                     */
+    int64_t batch, num_heads, num_kv_heads, seq_q, seq_kv, head_dim;
+    int64_t q_sb, q_sh, q_ss;
+    int64_t k_sb, k_sh, k_ss;
+    int64_t v_sb, v_sh, v_ss;
+    int64_t o_sb, o_sh, o_ss;
+    float scale;      /* multiplies Q.K; must be > 0                                              */
+    int32_t causal;   /* bottom-right aligned: key j visible from query i when j <= i + diagonal  */
+    int32_t return_lse;
+    int64_t diagonal; /* seq_kv - seq_q for causal, ignored otherwise                             */
+    int32_t dtype_id; /* SCA_DTYPE_F16 or SCA_DTYPE_BF16                                          */
+} ScaFlashFwdParams;
+
+SCA_ABI int sca_launch_flash_fwd(const ScaFlashFwdParams* params, void* stream);
+
+/* Shared-memory bytes of one flash tile (replaces FlashSmemBytesFor, flash_fwd_kernel.cuh:56).
+ * On sm_100a: Q tile + `stages` K tiles + `stages` V tiles, unpadded (TMA 128B swizzle needs no
+ * row padding) + 1 KiB of barriers and alignment slack. Returns -1 for a non-positive argument. */
+SCA_ABI long long sca_flash_smem_bytes_for(int head_dim, long long elem_bytes, int block_m,
+                                           int block_n, int stages);
+
+/* ------------------------------------------------------------------------------------------ */
+/* split-K decode (seq_q = 1) - replaces sca::cuda::LaunchDecodeSplitK / DecodeFwdParams          */
+/* (src/backends/decode/decode_splitk.cuh:23-57, decode_splitk.cu:229-253)                        */
+/* ------------------------------------------------------------------------------------------ */
+typedef struct ScaDecodeStrides {
+    int64_t s_b, s_h, s_s;
+} ScaDecodeStrides;
+
+typedef struct ScaDecodeFwdParams {
+    const void* q;      /* [batch, heads, 1, D]                                                  */
+    const void* k;      /* contiguous: [batch, kv_heads, seq_kv, D] through k_stride;            */
+    const void* v;      /* paged: origin of one layer's pool [blocks, block_size, kv_heads, D]   */
+    void* out;          /* [batch, heads, 1, D] through o_stride                                  */
+    float* partial_m;   /* [batch*heads*num_splits]      running max (natural units, scaled)      */
+    float* partial_l;   /* [batch*heads*num_splits]      sum of exp(s - m)                        */
+    float* partial_o;   /* [batch*heads*num_splits, D]   sum of exp(s - m) * V (unnormalised)     */
+    int64_t batch, num_heads, num_kv_heads, seq_kv, head_dim, num_splits;
+    ScaDecodeStrides q_stride, k_stride, v_stride, o_stride;
+    float scale;
+    int32_t dtype;      /* SCA_DTYPE_*                                                            */
+    /* page-table indirection; page_table == NULL selects the contiguous path */
+    const int32_t* page_table; /* [batch, max_blocks_per_seq], -1 = unmapped (weight 0)           */
+    int64_t block_size, max_blocks_per_seq, num_kv_blocks;
+    const int32_t* seq_lens;   /* [batch] or NULL (= seq_kv for every sequence)                   */
+} ScaDecodeFwdParams;
+
+/* partial kernel + merge kernel on `stream` */
+SCA_ABI int sca_launch_decode_splitk(const ScaDecodeFwdParams* params, void* stream);
+/* same, but requires the page-table fields (decode_splitk.cu:245-253) */
+SCA_ABI int sca_launch_decode_splitk_paged(const ScaDecodeFwdParams* params, void* stream);
+
+/* paged attention - replaces sca::cuda::LaunchPagedAttention / PagedDecodeParams
+ * (src/backends/paged/paged_attention.cuh:21-32, paged_attention.cu:12-22) */
+typedef struct ScaPagedDecodeParams {
+    ScaDecodeFwdParams base;
+    const int32_t* page_table;
+    int64_t block_size, max_blocks_per_seq, num_kv_blocks;
+} ScaPagedDecodeParams;
+
+SCA_ABI int sca_launch_paged_attention(const ScaPagedDecodeParams* params, void* stream);
+
+/* Sequence-split decode across GPUs (no counterpart in the reference, which is single-GPU).
+ * sca_launch_decode_triples runs the partial kernel and merges this GPU's splits WITHOUT the
+ * final normalisation: triples[(b*heads + h) * (2 + D)] = { m, l, O[D] } (fp32). After the
+ * triples of all ranks have been gathered ([ranks][batch*heads][2 + D]),
+ * sca_launch_merge_triples applies the same merge rule (decode_splitk.cu:143-182) across ranks
+ * and writes the normalised output. `out_dtype` is SCA_DTYPE_*. */
+SCA_ABI int sca_launch_decode_triples(const ScaDecodeFwdParams* params, float* triples, void* stream);
+SCA_ABI int sca_launch_merge_triples(const float* gathered, int64_t ranks, int64_t rows,
+                                     int64_t head_dim, void* out, int32_t out_dtype, void* stream);
+
+/* ------------------------------------------------------------------------------------------ */
+/* reference-level backends kept for API completeness (functional, not tuned):                   */
+/* one SIMT kernel serves LaunchNaiveForward (src/backends/naive/attention_naive.cuh:60) and      */
+/* LaunchTiledForward (src/backends/tiled/attention_tiled.cuh:57) and the fp32 decode case.       */
+/* Same parameter block as the flash entry; dtype_id may also be SCA_DTYPE_F32.                   */
+/* ------------------------------------------------------------------------------------------ */
+SCA_ABI int sca_launch_simt_forward(const ScaFlashFwdParams* params, void* stream);
+
+/* ------------------------------------------------------------------------------------------ */
+/* KV cache data movement - replaces LaunchKvAppend / LaunchKvResetBlock / LaunchKvGather         */
+/* (src/kv_cache/kv_cache_kernels.cuh:20-33, kv_cache_layout.cuh:24-38)                           */
+/* ------------------------------------------------------------------------------------------ */
+typedef struct ScaKvCacheShape {
+    int64_t num_blocks, block_size, num_kv_heads, head_dim;
+} ScaKvCacheShape;
+
+/* rows [num_tokens, kv_heads, D] -> slot = block * block_size + offset; slot < 0 and
+ * block >= num_blocks are skipped */
+SCA_ABI int sca_launch_kv_append(void* layer_k, void* layer_v, const void* k_new, const void* v_new,
+                                 const int32_t* slot_mapping, int64_t num_tokens,
+                                 const ScaKvCacheShape* shape, int64_t elem_bytes, void* stream);
+/* zeroes the listed blocks of K and V; ids < 0 or >= num_blocks are skipped */
+SCA_ABI int sca_launch_kv_reset_block(void* layer_k, void* layer_v, const int32_t* block_ids,
+                                      int64_t num_blocks, const ScaKvCacheShape* shape,
+                                      int64_t elem_bytes, void* stream);
+/* copies the listed blocks into a contiguous buffer; invalid ids gather zeros */
+SCA_ABI int sca_launch_kv_gather(const void* layer, const int32_t* block_ids, int64_t num_blocks,
+                                 void* out, const ScaKvCacheShape* shape, int64_t elem_bytes,
+                                 void* stream);
+
+/* Multi-sequence append (no counterpart in the reference, whose PagedKVCache::AppendTokens issues
+ * one launch and one blocking 4-byte upload per sequence, src/kv_cache/paged_kv_cache.cpp:52-142).
+ * One new token per sequence: slot = page_table[s, pos/bs] * bs + pos % bs with pos = seq_lens[s] - 1
+ * (seq_lens already includes the new token). Sequences whose page is unmapped are skipped. */
+SCA_ABI int sca_launch_kv_append_batched(void* layer_k, void* layer_v, const void* k_new,
+                                         const void* v_new, const int32_t* page_table,
+                                         const int32_t* seq_lens, int64_t num_seqs,
+                                         int64_t max_blocks_per_seq, const ScaKvCacheShape* shape,
+                                         int64_t elem_bytes, void* stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* SCA_B200_H_ */

@@ -1,7 +1,8 @@
 """ctypes bindings for the CPU oracle (oracle/liboracle.so) and, when it has been built, for the
 reference's own host code (oracle/_ref/libsca_ref.so).
 
-Test infrastructure only: nothing under the product package imports this module.
+Test infrastructure only: the test suite, the smoke check and the benchmark's CPU-baseline leg use it;
+nothing under the product package imports this module.
 """
 from __future__ import annotations
 
@@ -11,8 +12,8 @@ import subprocess
 
 import numpy as np
 
-ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
-ORACLE_DIR = os.path.join(ROOT, "oracle")
+ORACLE_DIR = os.path.dirname(os.path.abspath(__file__))
+ROOT = os.path.dirname(ORACLE_DIR)
 ORACLE_SO = os.path.join(ORACLE_DIR, "liboracle.so")
 REF_SO = os.path.join(ORACLE_DIR, "_ref", "libsca_ref.so")
 
