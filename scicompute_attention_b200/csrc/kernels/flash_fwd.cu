@@ -1,5 +1,542 @@
-// Flash prefill entry point (placeholder body until the tcgen05 kernel lands in this file).
+// Flash prefill for sm_100a: O = softmax(scale * Q K^T + mask) V with the score matrix kept on chip.
+//
+// Stands in for the reference's flash_fwd_kernel (src/backends/flash/flash_fwd_impl.cuh:45-279, an
+// sm_80 mma.sync + ldmatrix + cp.async design with 64x64 tiles and one CTA-wide barrier pair per
+// tile). Same arithmetic contract - fp16/bf16 inputs, fp32 accumulation, online softmax through
+// exp2, bottom-right aligned causal mask, GQA, optional log-sum-exp - on a Blackwell execution plan:
+//
+//   * one CTA owns 256 query rows of one (batch, head): two 128-row tiles that ping-pong, so the
+//     tensor core works on one tile while the other tile's softmax runs;
+//   * warp 0 is the TMA producer: Q tiles once, then K_j, V_j, K_j+1, ... into a ring of 128-byte
+//     swizzled shared-memory slots, each guarded by a full/empty mbarrier pair. Loads are plain
+//     per-CTA tensor loads (no cluster multicast); K/V reuse between the CTAs of a kv head comes
+//     from L2. Rows past the end of a sequence are zero-filled by the TMA unit;
+//   * warp 1 issues every tcgen05.mma from one thread: S_t = Q_t K_j^T (both operands in shared
+//     memory, K-major) into tensor memory, and O_t += P_t V_j with P_t read from tensor memory and
+//     V_j as an MN-major shared-memory operand (no transposition of V anywhere);
+//   * warps 4-7 and 8-11 are the two softmax groups, one thread per query row: they read their S row
+//     from tensor memory, keep the running max / sum in registers, write P back over S as packed
+//     16-bit values, and rescale O in tensor memory only when the running max moved by more than
+//     2^8 (the final division by the row sum absorbs the stale reference point exactly);
+//   * tensor memory: S_0 | S_1 | O_0 | O_1, 128 (or D) fp32 columns each, 512 columns in total.
+//
+// Every wait on an mbarrier is bounded (sm100.cuh): on expiry the role raises a CTA-wide abort flag,
+// the kernel records a code in a host-visible word, frees its tensor memory and returns.
+//
+// FLOPs per (query, key) pair that is visible: 4 * D. Algorithmic HBM bytes: Q + K + V + O once.
+#include <cuda.h>
+
+#include <mutex>
+#include <type_traits>
+
 #include "common.cuh"
+#include "sm100.cuh"
+
+namespace sca_b200 {
+namespace {
+
+using namespace sm100;
+
+constexpr int kBlockM = 128;
+constexpr int kBlockN = 128;
+constexpr int kQTiles = 2;
+constexpr int kFlashThreads = 384;   // warp 0 TMA, 1 MMA, 2 TMEM owner, 3 idle, 4-7 / 8-11 softmax
+constexpr int kTmemColumns = 512;
+constexpr float kRescaleThreshold = 8.0f;  // log2 domain: P stays <= 2^8
+
+template <int DP>
+struct FlashGeom {
+    static constexpr int kKBlocks = DP / 64;              // 64-element (128-byte) column blocks
+    static constexpr int kBlockBytes = 128 * 128;          // 128 rows x 128 bytes
+    static constexpr int kTileBytes = kKBlocks * kBlockBytes;
+    static constexpr int kSlots = (DP == 128) ? 5 : 8;     // K/V ring
+    static constexpr int kBarrierBytes = 256;
+    static constexpr int kSmemBytes = 1024 + kQTiles * kTileBytes + kSlots * kTileBytes + kBarrierBytes;
+    static constexpr int kSCol = 0;                        // S_t at kSCol + t * 128
+    static constexpr int kOCol = 256;                      // O_t at kOCol + t * DP
+    static_assert(DP == 64 || DP == 128, "padded head dim");
+    static_assert(kSmemBytes <= 232448, "exceeds the 227 KiB per-CTA limit");
+};
+
+struct FlashKernelParams {
+    void* out;
+    float* lse;
+    float* debug_s;  // optional: raw S of the first KV tile, [ctas][2][128][128] fp32 (tests only)
+    int* error_word; // host-visible; non-zero after a wait expired
+    int seq_q, seq_kv, heads, kv_heads, head_dim, batch;
+    int64_t o_sb, o_sh, o_ss;
+    float scale_log2;
+    int causal;
+    int diagonal;
+    int m_blocks;
+};
+
+__device__ __forceinline__ int TilesFor(const FlashKernelParams& p, int m0) {
+    if (m0 >= p.seq_q) return 0;
+    int64_t limit = p.seq_kv;
+    if (p.causal) limit = min(limit, static_cast<int64_t>(m0) + kBlockM + p.diagonal);
+    if (limit <= 0) return 0;
+    return static_cast<int>((limit + kBlockN - 1) / kBlockN);
+}
+
+template <typename T, int DP>
+__global__ void __launch_bounds__(kFlashThreads, 1)
+flash_fwd_sm100_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
+                       const __grid_constant__ CUtensorMap map_v, const FlashKernelParams p) {
+    using G = FlashGeom<DP>;
+    extern __shared__ unsigned char smem_raw[];
+    const uint32_t smem_base = (SmemAddr(smem_raw) + 1023u) & ~1023u;
+    unsigned char* smem = smem_raw + (smem_base - SmemAddr(smem_raw));
+
+    const uint32_t q_smem = smem_base;
+    const uint32_t ring_smem = smem_base + kQTiles * G::kTileBytes;
+    const uint32_t bar_base = ring_smem + G::kSlots * G::kTileBytes;
+    auto bar = [&](int i) { return bar_base + 8u * i; };
+    // barrier indices
+    constexpr int kQFull = 0;                       // [2]
+    constexpr int kKvFull = 2;                      // [kSlots]
+    constexpr int kKvEmpty = kKvFull + G::kSlots;   // [kSlots]
+    constexpr int kSFull = kKvEmpty + G::kSlots;    // [2]
+    constexpr int kPFull = kSFull + 2;              // [2]
+    constexpr int kODone = kPFull + 2;              // [2]
+    constexpr int kNumBars = kODone + 2;
+    static_assert(kNumBars * 8 + 16 <= G::kBarrierBytes, "barrier area too small");
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(smem + (bar_base - smem_base) + kNumBars * 8);
+    volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+
+    const int warp = threadIdx.x >> 5;
+    const int lane = threadIdx.x & 31;
+
+    // ---- which work does this CTA own (heaviest causal tiles first) --------------------------------
+    const int bh_count = p.batch * p.heads;
+    const int mb = p.m_blocks - 1 - static_cast<int>(blockIdx.x) / bh_count;
+    const int bh = static_cast<int>(blockIdx.x) % bh_count;
+    const int b = bh / p.heads;
+    const int h = bh % p.heads;
+    const int h_kv = h / (p.heads / p.kv_heads);
+    const int m0[2] = {(mb * kQTiles) * kBlockM, (mb * kQTiles + 1) * kBlockM};
+    const int ntiles[2] = {TilesFor(p, m0[0]), TilesFor(p, m0[1])};
+    const int n_max = max(ntiles[0], ntiles[1]);
+
+    if (threadIdx.x == 0) {
+        for (int i = 0; i < 2; ++i) MbarInit(bar(kQFull + i), 1);
+        for (int i = 0; i < G::kSlots; ++i) {
+            MbarInit(bar(kKvFull + i), 1);
+            MbarInit(bar(kKvEmpty + i), 1);
+        }
+        for (int i = 0; i < 2; ++i) {
+            MbarInit(bar(kSFull + i), 1);
+            MbarInit(bar(kPFull + i), 128);
+            MbarInit(bar(kODone + i), 1);
+        }
+        *abort_flag = 0;
+        FenceBarrierInit();
+    }
+    if (warp == 2) {
+        TmemAlloc(SmemAddr(tmem_slot), kTmemColumns);
+        TmemRelinquish();
+    }
+    TcFenceBefore();
+    __syncthreads();
+    TcFenceAfter();
+    const uint32_t tmem_base = *tmem_slot;
+
+    bool failed = false;
+
+    if (warp == 0) {
+        // ================================ TMA producer =============================================
+        if (lane == 0) {
+            PrefetchTensorMap(&map_q);
+            PrefetchTensorMap(&map_k);
+            PrefetchTensorMap(&map_v);
+            for (int t = 0; t < kQTiles; ++t) {
+                if (ntiles[t] == 0) continue;
+                MbarExpectTx(bar(kQFull + t), G::kTileBytes);
+                for (int kb = 0; kb < G::kKBlocks; ++kb) {
+                    TmaLoad4D(q_smem + t * G::kTileBytes + kb * G::kBlockBytes, &map_q, bar(kQFull + t), kb * 64,
+                              m0[t], h, b);
+                }
+            }
+            const int loads = 2 * n_max;  // K_0, V_0, K_1, V_1, ...
+            int slot = 0;
+            uint32_t phase = 0;
+            for (int it = 0; it < loads; ++it) {
+                if (!MbarWait(bar(kKvEmpty + slot), phase ^ 1u, abort_flag)) {
+                    failed = true;
+                    break;
+                }
+                MbarExpectTx(bar(kKvFull + slot), G::kTileBytes);
+                const CUtensorMap* map = (it & 1) ? &map_v : &map_k;
+                const int row0 = (it >> 1) * kBlockN;
+                for (int kb = 0; kb < G::kKBlocks; ++kb) {
+                    TmaLoad4D(ring_smem + slot * G::kTileBytes + kb * G::kBlockBytes, map, bar(kKvFull + slot),
+                              kb * 64, row0, h_kv, b);
+                }
+                if (++slot == G::kSlots) {
+                    slot = 0;
+                    phase ^= 1u;
+                }
+            }
+        }
+    } else if (warp == 1) {
+        // ================================ MMA issuer ================================================
+        if (lane == 0) {
+            constexpr uint32_t fmt = std::is_same<T, __half>::value ? kFmtF16 : kFmtBf16;
+            constexpr uint32_t idesc_s = MakeInstrDesc(fmt, 0, 0, kBlockM, kBlockN);  // Q K^T: both K-major
+            constexpr uint32_t idesc_o = MakeInstrDesc(fmt, 0, 1, kBlockM, DP);       // P V: V is MN-major
+            auto issue_s = [&](int t, int slot) {
+                const uint32_t a0 = q_smem + t * G::kTileBytes;
+                const uint32_t b0 = ring_smem + slot * G::kTileBytes;
+#pragma unroll
+                for (int ks = 0; ks < DP / 16; ++ks) {
+                    const uint32_t off = (ks >> 2) * G::kBlockBytes + (ks & 3) * 32;
+                    MmaSS(tmem_base + G::kSCol + t * kBlockN, MakeSmemDesc(a0 + off, 16, 1024),
+                          MakeSmemDesc(b0 + off, 16, 1024), idesc_s, ks > 0 ? 1u : 0u);
+                }
+            };
+            auto issue_pv = [&](int t, int slot, bool first) {
+                const uint32_t b0 = ring_smem + slot * G::kTileBytes;
+#pragma unroll
+                for (int ks = 0; ks < kBlockN / 16; ++ks) {
+                    MmaTS(tmem_base + G::kOCol + t * DP, tmem_base + G::kSCol + t * kBlockN + ks * 8,
+                          MakeSmemDesc(b0 + ks * 2048, G::kBlockBytes, 1024), idesc_o, (!first || ks > 0) ? 1u : 0u);
+                }
+            };
+            // ring position of load number `it` (K_j = 2j, V_j = 2j + 1)
+            auto slot_of = [&](int it) { return it % G::kSlots; };
+            auto phase_of = [&](int it) { return static_cast<uint32_t>((it / G::kSlots) & 1); };
+
+            bool ok = true;
+            for (int t = 0; t < kQTiles && ok; ++t) {
+                if (ntiles[t] > 0) ok = MbarWait(bar(kQFull + t), 0, abort_flag);
+            }
+            if (ok && n_max > 0) {
+                ok = MbarWait(bar(kKvFull + slot_of(0)), phase_of(0), abort_flag);
+                if (ok) {
+                    TcFenceAfter();
+                    for (int t = 0; t < kQTiles; ++t) {
+                        if (ntiles[t] > 0) {
+                            issue_s(t, slot_of(0));
+                            MmaCommit(bar(kSFull + t));
+                        }
+                    }
+                    MmaCommit(bar(kKvEmpty + slot_of(0)));
+                }
+            }
+            for (int j = 0; j < n_max && ok; ++j) {
+                const int it_v = 2 * j + 1;
+                const int it_k = 2 * j + 2;
+                ok = MbarWait(bar(kKvFull + slot_of(it_v)), phase_of(it_v), abort_flag);
+                if (ok && j + 1 < n_max) ok = MbarWait(bar(kKvFull + slot_of(it_k)), phase_of(it_k), abort_flag);
+                if (!ok) break;
+                for (int t = 0; t < kQTiles; ++t) {
+                    if (j >= ntiles[t]) continue;
+                    ok = MbarWait(bar(kPFull + t), static_cast<uint32_t>(j & 1), abort_flag);
+                    if (!ok) break;
+                    TcFenceAfter();
+                    issue_pv(t, slot_of(it_v), j == 0);
+                    MmaCommit(bar(kODone + t));
+                    if (j + 1 < ntiles[t]) {
+                        issue_s(t, slot_of(it_k));
+                        MmaCommit(bar(kSFull + t));
+                    }
+                }
+                if (!ok) break;
+                MmaCommit(bar(kKvEmpty + slot_of(it_v)));
+                if (j + 1 < n_max) MmaCommit(bar(kKvEmpty + slot_of(it_k)));
+            }
+            failed = !ok;
+        }
+    } else if (warp >= 4) {
+        // ================================ softmax groups ============================================
+        const int t = (warp - 4) >> 2;
+        const int quad = warp & 3;
+        const int row_in_tile = quad * 32 + lane;
+        const int row = m0[t] + row_in_tile;
+        const uint32_t lane_bits = static_cast<uint32_t>(quad * 32) << 16;
+        const uint32_t s_addr = tmem_base + lane_bits + G::kSCol + t * kBlockN;
+        const uint32_t o_addr = tmem_base + lane_bits + G::kOCol + t * DP;
+        const int n_t = ntiles[t];
+
+        float m_ref = -CUDART_INF_F;  // reference point of the exponentials (log2 domain)
+        float l_sum = 0.0f;
+        bool ok = true;
+
+        for (int j = 0; j < n_t; ++j) {
+            ok = __all_sync(0xffffffffu, MbarWait(bar(kSFull + t), static_cast<uint32_t>(j & 1), abort_flag));
+            if (!ok) break;
+            TcFenceAfter();
+            float s[kBlockN];
+#pragma unroll
+            for (int cblk = 0; cblk < kBlockN / 32; ++cblk) {
+                uint32_t r[32];
+                TmemLd32(s_addr + cblk * 32, r);
+#pragma unroll
+                for (int i = 0; i < 32; ++i) s[cblk * 32 + i] = __uint_as_float(r[i]);
+            }
+            TmemWaitLd();
+            if (p.debug_s != nullptr && j == 0) {
+                float* dst = p.debug_s + ((static_cast<size_t>(blockIdx.x) * 2 + t) * kBlockM + row_in_tile) * kBlockN;
+#pragma unroll
+                for (int i = 0; i < kBlockN; ++i) dst[i] = s[i];
+            }
+            // scale into the log2 domain and mask
+            const int col0 = j * kBlockN;
+            const int kv_limit = p.seq_kv - col0;                                // columns >= kv_limit do not exist
+            const int causal_limit = p.causal ? (row + p.diagonal - col0 + 1) : kBlockN;  // columns >= limit are masked
+            const int limit = min(kv_limit, causal_limit);
+            float mx = -CUDART_INF_F;
+            if (limit >= kBlockN) {
+#pragma unroll
+                for (int i = 0; i < kBlockN; ++i) {
+                    s[i] *= p.scale_log2;
+                    mx = fmaxf(mx, s[i]);
+                }
+            } else {
+#pragma unroll
+                for (int i = 0; i < kBlockN; ++i) {
+                    s[i] = (i < limit) ? s[i] * p.scale_log2 : -CUDART_INF_F;
+                    mx = fmaxf(mx, s[i]);
+                }
+            }
+            const float m_new = fmaxf(m_ref, mx);
+            // Move the reference point only when it is far off; O and l are rescaled to match.
+            const bool move = (j == 0) || (m_new - m_ref > kRescaleThreshold);
+            if (j > 0 && __any_sync(0xffffffffu, move)) {
+                ok = __all_sync(0xffffffffu, MbarWait(bar(kODone + t), static_cast<uint32_t>((j - 1) & 1), abort_flag));
+                if (!ok) break;
+                TcFenceAfter();
+                const float alpha = move ? Exp2(m_ref - m_new) : 1.0f;  // m_ref = -inf -> 0
+#pragma unroll
+                for (int cblk = 0; cblk < DP / 32; ++cblk) {
+                    uint32_t r[32];
+                    TmemLd32(o_addr + cblk * 32, r);
+                    TmemWaitLd();
+#pragma unroll
+                    for (int i = 0; i < 32; ++i) r[i] = __float_as_uint(__uint_as_float(r[i]) * alpha);
+                    TmemSt32(o_addr + cblk * 32, r);
+                }
+                l_sum *= alpha;
+            }
+            if (move) m_ref = m_new;
+            const float m_eff = (m_ref == -CUDART_INF_F) ? 0.0f : m_ref;
+            float part = 0.0f;
+#pragma unroll
+            for (int i = 0; i < kBlockN; ++i) {
+                s[i] = Exp2(s[i] - m_eff);
+                part += s[i];
+            }
+            l_sum += part;
+            // P (16-bit pairs) over the first 64 columns of S_t
+#pragma unroll
+            for (int cblk = 0; cblk < kBlockN / 64; ++cblk) {
+                uint32_t r[32];
+#pragma unroll
+                for (int i = 0; i < 32; ++i) r[i] = Pack2<T>(s[cblk * 64 + 2 * i], s[cblk * 64 + 2 * i + 1]);
+                TmemSt32(s_addr + cblk * 32, r);
+            }
+            TmemWaitSt();
+            TcFenceBefore();
+            MbarArrive(bar(kPFull + t));
+        }
+
+        // ---- epilogue: O / l -> global, optional LSE ------------------------------------------------
+        if (ok && n_t > 0) {
+            ok = __all_sync(0xffffffffu, MbarWait(bar(kODone + t), static_cast<uint32_t>((n_t - 1) & 1), abort_flag));
+            if (ok) {
+                TcFenceAfter();
+                const float inv = l_sum > 0.0f ? 1.0f / l_sum : 0.0f;
+                T* o_row = reinterpret_cast<T*>(p.out) + b * p.o_sb + h * p.o_sh + static_cast<int64_t>(row) * p.o_ss;
+#pragma unroll
+                for (int cblk = 0; cblk < DP / 32; ++cblk) {
+                    uint32_t r[32];
+                    TmemLd32(o_addr + cblk * 32, r);
+                    TmemWaitLd();
+                    if (row < p.seq_q) {
+#pragma unroll
+                        for (int v8 = 0; v8 < 4; ++v8) {
+                            const int d0 = cblk * 32 + v8 * 8;
+                            if (d0 < p.head_dim) {
+                                uint4 pk;
+                                pk.x = Pack2<T>(__uint_as_float(r[v8 * 8 + 0]) * inv, __uint_as_float(r[v8 * 8 + 1]) * inv);
+                                pk.y = Pack2<T>(__uint_as_float(r[v8 * 8 + 2]) * inv, __uint_as_float(r[v8 * 8 + 3]) * inv);
+                                pk.z = Pack2<T>(__uint_as_float(r[v8 * 8 + 4]) * inv, __uint_as_float(r[v8 * 8 + 5]) * inv);
+                                pk.w = Pack2<T>(__uint_as_float(r[v8 * 8 + 6]) * inv, __uint_as_float(r[v8 * 8 + 7]) * inv);
+                                *reinterpret_cast<uint4*>(o_row + d0) = pk;
+                            }
+                        }
+                    }
+                }
+                if (p.lse != nullptr && row < p.seq_q) {
+                    p.lse[(static_cast<int64_t>(b) * p.heads + h) * p.seq_q + row] =
+                        l_sum > 0.0f ? (m_ref + log2f(l_sum)) * kLn2 : -CUDART_INF_F;
+                }
+            }
+        }
+        failed = !ok;
+    }
+
+    if (failed && p.error_word != nullptr) *p.error_word = 1 + warp;
+
+    // ---- teardown ------------------------------------------------------------------------------------
+    TcFenceBefore();
+    __syncthreads();
+    if (warp == 2) {
+        TcFenceAfter();
+        TmemDealloc(tmem_base, kTmemColumns);
+    }
+}
+
+// ---- host side -----------------------------------------------------------------------------------------
+using EncodeTiledFn = CUresult (*)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                   const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                   CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeTiledFn GetEncodeTiled() {
+    static EncodeTiledFn fn = [] {
+        void* sym = nullptr;
+        cudaDriverEntryPointQueryResult q;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &sym, cudaEnableDefault, &q) != cudaSuccess ||
+            q != cudaDriverEntryPointSuccess) {
+            cudaGetLastError();
+            sym = nullptr;
+        }
+        return reinterpret_cast<EncodeTiledFn>(sym);
+    }();
+    return fn;
+}
+
+// [batch][heads][seq][D] through element strides (sb, sh, ss); box = 64 x 128 elements, 128B swizzle,
+// out-of-range elements read as zero.
+int MakeMap(CUtensorMap* map, const void* base, int dtype_id, int64_t d, int64_t seq, int64_t heads, int64_t batch,
+            int64_t ss, int64_t sh, int64_t sb, const char* what) {
+    EncodeTiledFn encode = GetEncodeTiled();
+    if (encode == nullptr) return Fail(SCA_CUDA_ERROR, "flash attention: cuTensorMapEncodeTiled is unavailable");
+    const cuuint64_t dims[4] = {static_cast<cuuint64_t>(d), static_cast<cuuint64_t>(seq),
+                                static_cast<cuuint64_t>(heads), static_cast<cuuint64_t>(batch)};
+    const cuuint64_t strides[3] = {static_cast<cuuint64_t>(ss) * 2, static_cast<cuuint64_t>(sh) * 2,
+                                   static_cast<cuuint64_t>(sb) * 2};
+    const cuuint32_t box[4] = {64, 128, 1, 1};
+    const cuuint32_t elem[4] = {1, 1, 1, 1};
+    const CUtensorMapDataType type =
+        dtype_id == SCA_DTYPE_F16 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT16 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16;
+    const CUresult rc = encode(map, type, 4, const_cast<void*>(base), dims, strides, box, elem,
+                               CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                               CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (rc != CUDA_SUCCESS) {
+        return Fail(SCA_INVALID_ARGUMENT, std::string("flash attention: tensor map for ") + what +
+                                              " rejected (CUresult " + std::to_string(static_cast<int>(rc)) +
+                                              "); base must be 16-byte aligned and strides multiples of 8 elements");
+    }
+    return SCA_OK;
+}
+
+// One host-visible word per process that kernels set when a bounded wait expires.
+int* ErrorWordDevicePtr(int** host_view) {
+    static int* host = nullptr;
+    static int* dev = nullptr;
+    static std::once_flag once;
+    std::call_once(once, [] {
+        if (cudaHostAlloc(reinterpret_cast<void**>(&host), sizeof(int), cudaHostAllocMapped | cudaHostAllocPortable) !=
+            cudaSuccess) {
+            cudaGetLastError();
+            host = nullptr;
+            return;
+        }
+        *host = 0;
+        if (cudaHostGetDevicePointer(reinterpret_cast<void**>(&dev), host, 0) != cudaSuccess) {
+            cudaGetLastError();
+            dev = nullptr;
+        }
+    });
+    if (host_view != nullptr) *host_view = host;
+    return dev;
+}
+
+template <typename T, int DP>
+int LaunchFlash(const ScaFlashFwdParams& f, float* debug_s, cudaStream_t stream) {
+    using G = FlashGeom<DP>;
+    CUtensorMap map_q, map_k, map_v;
+    if (int rc = MakeMap(&map_q, f.q, f.dtype_id, f.head_dim, f.seq_q, f.num_heads, f.batch, f.q_ss, f.q_sh, f.q_sb, "q")) return rc;
+    if (int rc = MakeMap(&map_k, f.k, f.dtype_id, f.head_dim, f.seq_kv, f.num_kv_heads, f.batch, f.k_ss, f.k_sh, f.k_sb, "k")) return rc;
+    if (int rc = MakeMap(&map_v, f.v, f.dtype_id, f.head_dim, f.seq_kv, f.num_kv_heads, f.batch, f.v_ss, f.v_sh, f.v_sb, "v")) return rc;
+
+    FlashKernelParams p{};
+    p.out = f.out;
+    p.lse = f.return_lse ? f.lse : nullptr;
+    p.debug_s = debug_s;
+    int* host_word = nullptr;
+    p.error_word = ErrorWordDevicePtr(&host_word);
+    if (host_word != nullptr && *host_word != 0) {
+        const int code = *host_word;
+        *host_word = 0;
+        return Fail(SCA_CUDA_ERROR, "flash attention: an earlier launch gave up waiting on a barrier (role " +
+                                        std::to_string(code) + "); its output is invalid");
+    }
+    p.seq_q = static_cast<int>(f.seq_q);
+    p.seq_kv = static_cast<int>(f.seq_kv);
+    p.heads = static_cast<int>(f.num_heads);
+    p.kv_heads = static_cast<int>(f.num_kv_heads);
+    p.head_dim = static_cast<int>(f.head_dim);
+    p.batch = static_cast<int>(f.batch);
+    p.o_sb = f.o_sb;
+    p.o_sh = f.o_sh;
+    p.o_ss = f.o_ss;
+    p.scale_log2 = f.scale * kLog2e;
+    p.causal = f.causal ? 1 : 0;
+    p.diagonal = static_cast<int>(f.causal ? f.diagonal : 0);
+    p.m_blocks = static_cast<int>((f.seq_q + kQTiles * kBlockM - 1) / (kQTiles * kBlockM));
+    const int64_t ctas = static_cast<int64_t>(p.m_blocks) * p.batch * p.heads;
+    if (ctas <= 0 || ctas > 0x7fffffffLL) {
+        return Fail(SCA_INVALID_ARGUMENT, "flash attention: grid of " + std::to_string(ctas) + " blocks is out of range");
+    }
+    const void* fn = reinterpret_cast<const void*>(&flash_fwd_sm100_kernel<T, DP>);
+    if (int rc = EnsureDynamicSmem(fn, G::kSmemBytes, "flash_fwd_sm100_kernel")) return rc;
+    flash_fwd_sm100_kernel<T, DP><<<static_cast<unsigned>(ctas), kFlashThreads, G::kSmemBytes, stream>>>(map_q, map_k, map_v, p);
+    return CheckLaunch("flash_fwd_sm100_kernel", stream);
+}
+
+int ValidateFlash(const ScaFlashFwdParams* params) {
+    if (params == nullptr || params->q == nullptr || params->k == nullptr || params->v == nullptr ||
+        params->out == nullptr) {
+        return Fail(SCA_INVALID_ARGUMENT, "flash attention: null tensor pointer");
+    }
+    const ScaFlashFwdParams& f = *params;
+    if (f.dtype_id != SCA_DTYPE_F16 && f.dtype_id != SCA_DTYPE_BF16) {
+        return Fail(SCA_INVALID_ARGUMENT, "flash attention: only fp16/bf16 are instantiated (dtype_id=" +
+                                              std::to_string(f.dtype_id) + "); use the naive or tiled backend for FP32");
+    }
+    if (f.batch < 1 || f.num_heads < 1 || f.num_kv_heads < 1 || f.seq_q < 1 || f.seq_kv < 1 ||
+        f.num_heads % f.num_kv_heads != 0) {
+        return Fail(SCA_INVALID_ARGUMENT, "flash attention: invalid geometry");
+    }
+    if (f.seq_q > 0x7fffff00LL || f.seq_kv > 0x7fffff00LL) {
+        return Fail(SCA_INVALID_ARGUMENT, "flash attention: sequence length exceeds the 32-bit tile index range");
+    }
+    if (!(f.scale > 0.0f)) return Fail(SCA_INVALID_ARGUMENT, "flash attention: scale must be > 0");
+    if (f.return_lse && f.lse == nullptr) return Fail(SCA_INVALID_ARGUMENT, "flash attention: return_lse without a buffer");
+    if (!Aligned16(f.out) || f.o_sb % 8 != 0 || f.o_sh % 8 != 0 || f.o_ss % 8 != 0) {
+        return Fail(SCA_INVALID_ARGUMENT, "flash attention: out must be 16-byte aligned with strides that are multiples of 8 elements");
+    }
+    return SCA_OK;
+}
+
+template <typename T>
+int LaunchFlashTyped(const ScaFlashFwdParams& f, float* debug_s, cudaStream_t stream) {
+    // head dims that are not a multiple of 64 run on the next padded geometry: the TMA unit
+    // zero-fills the missing columns of Q, K and V, which leaves S and the real columns of O unchanged
+    switch (f.head_dim) {
+        case 32:
+        case 64: return LaunchFlash<T, 64>(f, debug_s, stream);
+        case 96:
+        case 128: return LaunchFlash<T, 128>(f, debug_s, stream);
+        default: break;
+    }
+    return Fail(SCA_INVALID_ARGUMENT, "flash attention: head_dim=" + std::to_string(f.head_dim) + " is not instantiated");
+}
+
+}  // namespace
+}  // namespace sca_b200
 
 using namespace sca_b200;
 
@@ -11,12 +548,20 @@ extern "C" long long sca_flash_smem_bytes_for(int head_dim, long long elem_bytes
     return q + 2 * kv + 1024;
 }
 
-extern "C" int sca_launch_flash_fwd(const ScaFlashFwdParams* params, void* stream) {
-    (void)stream;
+// Test hook (not declared in the public header): same launch with a raw-S dump of the first KV tile.
+extern "C" __attribute__((visibility("default"))) int sca_debug_flash_fwd(const ScaFlashFwdParams* params,
+                                                                          float* debug_s, void* stream) {
     ClearError();
-    if (params == nullptr || params->q == nullptr || params->k == nullptr || params->v == nullptr ||
-        params->out == nullptr) {
-        return Fail(SCA_INVALID_ARGUMENT, "flash attention: null tensor pointer");
-    }
-    return Fail(SCA_NOT_IMPLEMENTED, "flash attention: kernel not built yet");
+    if (int rc = ValidateFlash(params)) return rc;
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    return params->dtype_id == SCA_DTYPE_F16 ? LaunchFlashTyped<__half>(*params, debug_s, s)
+                                             : LaunchFlashTyped<__nv_bfloat16>(*params, debug_s, s);
+}
+
+extern "C" int sca_launch_flash_fwd(const ScaFlashFwdParams* params, void* stream) {
+    ClearError();
+    if (int rc = ValidateFlash(params)) return rc;
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    return params->dtype_id == SCA_DTYPE_F16 ? LaunchFlashTyped<__half>(*params, nullptr, s)
+                                             : LaunchFlashTyped<__nv_bfloat16>(*params, nullptr, s);
 }
