@@ -321,7 +321,7 @@ class FlashWorkload(Workload):
 
 
 WORKLOADS = {"flash": FlashWorkload, "decode": DecodeWorkload, "paged": PagedWorkload}
-DEFAULT_WORKLOAD = "decode"
+DEFAULT_WORKLOAD = "flash"
 
 
 # --------------------------------------------------------------------------------------------------
