@@ -162,6 +162,25 @@ SCA_ABI int sca_launch_decode_triples(const ScaDecodeFwdParams* params, float* t
 SCA_ABI int sca_launch_merge_triples(const float* gathered, int64_t ranks, int64_t rows,
                                      int64_t head_dim, void* out, int32_t out_dtype, void* stream);
 
+/* Allocation-free split-K decode. No counterpart in the reference.
+ *
+ * For callers that are not allowed to obtain device memory around the call: code running while a
+ * stream is being captured, serving loops that have handed every free byte of the GPU to their own
+ * pool (so a cudaMalloc would fail or stall the device), and hosts that forbid allocation after
+ * start-up. It computes exactly what sca_launch_decode_splitk computes, but ignores
+ * params->partial_m / partial_l / partial_o (they may be NULL) and keeps the split-K partials in a
+ * fixed array inside the library: 4 Mi floats (16 MiB) that every GPU using the library holds until
+ * the process ends. The call itself uses no cudaMalloc, cudaFree or allocating library routine.
+ *
+ * Limit: batch * num_heads * num_splits * (2 + head_dim) <= 4 194 304 floats, otherwise
+ * SCA_INVALID_ARGUMENT with the required size in the message.
+ * The first call on each device looks up the array's device address (one cudaGetSymbolAddress with
+ * that device current); make that first call before starting any stream capture.
+ * All calls share the one array and it keeps the previous call's contents; nothing in it has to start
+ * at zero because every (batch, head, split) entry is rewritten before it is read. Two calls whose
+ * kernels may overlap on the GPU (different streams without an ordering between them) race on it. */
+SCA_ABI int sca_launch_decode_splitk_static(const ScaDecodeFwdParams* params, void* stream);
+
 /* ------------------------------------------------------------------------------------------ */
 /* reference-level backends kept for API completeness (functional, not tuned):                   */
 /* one SIMT kernel serves LaunchNaiveForward (src/backends/naive/attention_naive.cuh:60) and      */

@@ -19,7 +19,7 @@ STATUS_NAMES = {0: "OK", 4: "InvalidArgument", 5: "NotImplemented", 100: "CudaEr
 EXPORTED_SYMBOLS = [
     "sca_last_error", "sca_probe_device", "sca_mem_get_info", "sca_launch_flash_fwd",
     "sca_flash_smem_bytes_for", "sca_launch_decode_splitk", "sca_launch_decode_splitk_paged",
-    "sca_launch_paged_attention", "sca_launch_decode_triples", "sca_launch_merge_triples",
+    "sca_launch_paged_attention", "sca_launch_decode_splitk_static", "sca_launch_decode_triples", "sca_launch_merge_triples",
     "sca_launch_simt_forward", "sca_launch_kv_append", "sca_launch_kv_reset_block",
     "sca_launch_kv_gather", "sca_launch_kv_append_batched",
 ]
@@ -105,6 +105,7 @@ def lib() -> C.CDLL:
     l.sca_launch_decode_splitk.argtypes = [C.POINTER(DecodeFwdParams), C.c_void_p]
     l.sca_launch_decode_splitk_paged.argtypes = [C.POINTER(DecodeFwdParams), C.c_void_p]
     l.sca_launch_paged_attention.argtypes = [C.POINTER(PagedDecodeParams), C.c_void_p]
+    l.sca_launch_decode_splitk_static.argtypes = [C.POINTER(DecodeFwdParams), C.c_void_p]
     l.sca_launch_decode_triples.argtypes = [C.POINTER(DecodeFwdParams), C.c_void_p, C.c_void_p]
     l.sca_launch_merge_triples.argtypes = [C.c_void_p, C.c_int64, C.c_int64, C.c_int64, C.c_void_p,
                                            C.c_int32, C.c_void_p]

@@ -21,6 +21,7 @@
 //
 // Algorithmic HBM traffic per token and kv head: 2 * D * sizeof(T) bytes (K row + V row), read once.
 #include <algorithm>
+#include <mutex>
 
 #include "common.cuh"
 
@@ -514,6 +515,46 @@ int LaunchDecodePartials(const ScaDecodeFwdParams& p, cudaStream_t stream) {
 
 }  // namespace sca_b200
 
+// ---- allocation-free variant ---------------------------------------------------------------------
+// Split-K partials for callers that must not allocate device memory live in this fixed array. Every
+// GPU that loads the library carries it until the process exits. In host code the name below is only
+// a host-side stand-in for the symbol, never a device address: the address a kernel may use comes
+// from cudaGetSymbolAddress, looked up once per device with that device current.
+namespace sca_b200 {
+namespace {
+
+constexpr int64_t kStaticScratchFloats = int64_t{4} << 20;  // 4 Mi floats = 16 MiB per GPU
+static __device__ __align__(256) float g_decode_static_scratch[kStaticScratchFloats];
+
+constexpr int kMaxDevices = 64;
+std::mutex g_static_scratch_mutex;
+float* g_static_scratch_ptr[kMaxDevices] = {};
+
+// Device address of the static scratch on the current device (looked up on first use per device).
+int StaticScratchFor(float** out) {
+    int device = 0;
+    cudaError_t err = cudaGetDevice(&device);
+    if (err != cudaSuccess) return FailCuda(err, "decode (static scratch): cudaGetDevice");
+    if (device < 0 || device >= kMaxDevices) {
+        return Fail(SCA_INVALID_ARGUMENT, "decode (static scratch): device index " + std::to_string(device) + " is out of range");
+    }
+    std::lock_guard<std::mutex> lock(g_static_scratch_mutex);
+    if (g_static_scratch_ptr[device] == nullptr) {
+        float* ptr = nullptr;
+        err = cudaGetSymbolAddress(reinterpret_cast<void**>(&ptr), g_decode_static_scratch);
+        if (err != cudaSuccess || ptr == nullptr) {
+            cudaGetLastError();
+            return FailCuda(err, "decode (static scratch): cudaGetSymbolAddress");
+        }
+        g_static_scratch_ptr[device] = ptr;
+    }
+    *out = g_static_scratch_ptr[device];
+    return SCA_OK;
+}
+
+}  // namespace
+}  // namespace sca_b200
+
 using namespace sca_b200;
 
 extern "C" int sca_launch_decode_splitk(const ScaDecodeFwdParams* params, void* stream) {
@@ -606,4 +647,32 @@ extern "C" int sca_launch_merge_triples(const float* gathered, int64_t ranks, in
         default: return Fail(SCA_INVALID_ARGUMENT, "merge triples: unsupported dtype id");
     }
     return CheckLaunch("decode_merge_kernel(ranks)", s);
+}
+
+// Allocation-free split-K decode: same kernels and same result as sca_launch_decode_splitk, with the
+// partials kept in the library's fixed 16 MiB device array instead of caller-provided scratch.
+extern "C" int sca_launch_decode_splitk_static(const ScaDecodeFwdParams* params, void* stream) {
+    ClearError();
+    if (params == nullptr) return Fail(SCA_INVALID_ARGUMENT, "decode: null parameter block");
+    ScaDecodeFwdParams p = *params;
+    if (p.batch < 1 || p.num_heads < 1 || p.num_splits < 1 || p.head_dim < 1) {
+        return Fail(SCA_INVALID_ARGUMENT, "decode (static scratch): batch/heads/num_splits/head_dim must be positive");
+    }
+    const int64_t base = p.batch * p.num_heads * p.num_splits;
+    const int64_t need = base * (2 + p.head_dim);
+    if (base > kStaticScratchFloats || need > kStaticScratchFloats) {
+        return Fail(SCA_INVALID_ARGUMENT,
+                    "decode (static scratch): batch*heads*num_splits*(2+head_dim) = " + std::to_string(need) +
+                        " floats exceeds the built-in scratch of " + std::to_string(kStaticScratchFloats) +
+                        " floats; use fewer splits or the entry point that takes caller scratch");
+    }
+    float* scratch = nullptr;
+    if (int rc = StaticScratchFor(&scratch)) return rc;
+    p.partial_m = scratch;
+    p.partial_l = scratch + base;
+    p.partial_o = scratch + 2 * base;
+    if (int rc = ValidateDecode(&p, true)) return rc;
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    if (int rc = LaunchDecodePartials(p, s)) return rc;
+    return LaunchMergeOut(p, s);
 }
