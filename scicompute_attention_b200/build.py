@@ -102,16 +102,38 @@ def build_host(force: bool = False, verbose: bool = False) -> str | None:
     if jobs or not os.path.exists(HOST_LIB) or not _newer(HOST_LIB, [KERNEL_LIB]):
         cuda_lib = os.path.join(os.path.dirname(os.path.dirname(_nvcc())), "lib64")
         _run([cxx, "-shared", "-o", HOST_LIB] + objs +
-             ["-L", PKG, "-l:libsca_b200.so", "-L", cuda_lib, "-lcudart", "-Wl,-rpath,$ORIGIN",
-              "-Wl,-rpath," + cuda_lib])
+             ["-L", PKG, "-l:libsca_b200.so", "-L", cuda_lib, "-lcudart_static", "-lrt", "-ldl", "-lpthread",
+              "-Wl,-rpath,$ORIGIN"])
     if verbose:
         print("built", HOST_LIB)
     return HOST_LIB
 
 
+def build_cpp_tests(force: bool = False, verbose: bool = False) -> str | None:
+    """tests/cpp/api_tests.cpp -> tests/cpp/api_tests (links the host library and, as the checker, the oracle)."""
+    src = os.path.join(ROOT, "tests", "cpp", "api_tests.cpp")
+    oracle_so = os.path.join(ROOT, "oracle", "liboracle.so")
+    if not os.path.exists(src) or not os.path.exists(HOST_LIB):
+        return None
+    if not os.path.exists(oracle_so):
+        subprocess.run(["make", "-C", os.path.join(ROOT, "oracle"), "-s"], check=True)
+    exe = os.path.join(ROOT, "tests", "cpp", "api_tests")
+    deps = [src, os.path.join(ROOT, "tests", "cpp", "mini_test.hpp"), HOST_LIB, oracle_so] + _headers()
+    if force or not _newer(exe, deps):
+        cxx = shutil.which("g++") or "g++"
+        _run([cxx, "-O1", "-std=c++20", "-Wall", "-I", INCLUDE, "-I", os.path.join(INCLUDE, "sci_infra"),
+              "-I", os.path.join(ROOT, "tests", "cpp"), src, "-o", exe, "-L", PKG, "-l:libsci_attention.so",
+              "-l:libsca_b200.so", "-L", os.path.join(ROOT, "oracle"), "-l:liboracle.so",
+              "-Wl,-rpath,$ORIGIN/../../scicompute_attention_b200", "-Wl,-rpath,$ORIGIN/../../oracle"])
+    if verbose:
+        print("built", exe)
+    return exe
+
+
 def build_all(force: bool = False, verbose: bool = False) -> None:
     build_kernels(force, verbose)
     build_host(force, verbose)
+    build_cpp_tests(force, verbose)
 
 
 if __name__ == "__main__":

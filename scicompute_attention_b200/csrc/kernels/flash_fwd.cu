@@ -38,23 +38,27 @@ namespace {
 using namespace sm100;
 
 constexpr int kBlockM = 128;
-constexpr int kBlockN = 128;
-constexpr int kQTiles = 2;
 constexpr int kFlashThreads = 384;   // warp 0 TMA, 1 MMA, 2 TMEM owner, 3 idle, 4-7 / 8-11 softmax
 constexpr int kTmemColumns = 512;
 constexpr float kRescaleThreshold = 8.0f;  // log2 domain: P stays <= 2^8
 
-template <int DP>
+// DP: padded head dim (64 / 128 / 256); QT: query tiles per CTA; BN: keys per KV tile.
+// 64 and 128 run two query tiles against 128-key tiles; 256 needs 256 TMEM columns for O, so it runs one
+// query tile against 64-key tiles (S 64 + O 256 columns).
+template <int DP, int QT, int BN>
 struct FlashGeom {
-    static constexpr int kKBlocks = DP / 64;              // 64-element (128-byte) column blocks
-    static constexpr int kBlockBytes = 128 * 128;          // 128 rows x 128 bytes
-    static constexpr int kTileBytes = kKBlocks * kBlockBytes;
-    static constexpr int kSlots = (DP == 128) ? 5 : 8;     // K/V ring
+    static constexpr int kKBlocks = DP / 64;               // 64-element (128-byte) column blocks per row
+    static constexpr int kQBlockBytes = kBlockM * 128;      // one column block of a query tile
+    static constexpr int kKvBlockBytes = BN * 128;          // one column block of a K or V tile
+    static constexpr int kQTileBytes = kKBlocks * kQBlockBytes;
+    static constexpr int kKvTileBytes = kKBlocks * kKvBlockBytes;
+    static constexpr int kSlots = (DP == 128) ? 5 : (DP == 64 ? 8 : 4);  // K/V ring
     static constexpr int kBarrierBytes = 256;
-    static constexpr int kSmemBytes = 1024 + kQTiles * kTileBytes + kSlots * kTileBytes + kBarrierBytes;
-    static constexpr int kSCol = 0;                        // S_t at kSCol + t * 128
-    static constexpr int kOCol = 256;                      // O_t at kOCol + t * DP
-    static_assert(DP == 64 || DP == 128, "padded head dim");
+    static constexpr int kSmemBytes = 1024 + QT * kQTileBytes + kSlots * kKvTileBytes + kBarrierBytes;
+    static constexpr int kSCol = 0;                         // S_t at kSCol + t * 128
+    static constexpr int kOCol = 256;                       // O_t at kOCol + t * DP
+    static_assert((DP == 64 || DP == 128) ? (QT == 2 && BN == 128) : (DP == 256 && QT == 1 && BN == 64), "geometry");
+    static_assert(kOCol + QT * DP <= kTmemColumns, "tensor memory budget");
     static_assert(kSmemBytes <= 232448, "exceeds the 227 KiB per-CTA limit");
 };
 
@@ -71,26 +75,27 @@ struct FlashKernelParams {
     int m_blocks;
 };
 
+template <int BN>
 __device__ __forceinline__ int TilesFor(const FlashKernelParams& p, int m0) {
     if (m0 >= p.seq_q) return 0;
     int64_t limit = p.seq_kv;
     if (p.causal) limit = min(limit, static_cast<int64_t>(m0) + kBlockM + p.diagonal);
     if (limit <= 0) return 0;
-    return static_cast<int>((limit + kBlockN - 1) / kBlockN);
+    return static_cast<int>((limit + BN - 1) / BN);
 }
 
-template <typename T, int DP>
+template <typename T, int DP, int QT, int BN>
 __global__ void __launch_bounds__(kFlashThreads, 1)
 flash_fwd_sm100_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
                        const __grid_constant__ CUtensorMap map_v, const FlashKernelParams p) {
-    using G = FlashGeom<DP>;
+    using G = FlashGeom<DP, QT, BN>;
     extern __shared__ unsigned char smem_raw[];
     const uint32_t smem_base = (SmemAddr(smem_raw) + 1023u) & ~1023u;
     unsigned char* smem = smem_raw + (smem_base - SmemAddr(smem_raw));
 
     const uint32_t q_smem = smem_base;
-    const uint32_t ring_smem = smem_base + kQTiles * G::kTileBytes;
-    const uint32_t bar_base = ring_smem + G::kSlots * G::kTileBytes;
+    const uint32_t ring_smem = smem_base + QT * G::kQTileBytes;
+    const uint32_t bar_base = ring_smem + G::kSlots * G::kKvTileBytes;
     auto bar = [&](int i) { return bar_base + 8u * i; };
     // barrier indices
     constexpr int kQFull = 0;                       // [2]
@@ -114,8 +119,8 @@ flash_fwd_sm100_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
     const int b = bh / p.heads;
     const int h = bh % p.heads;
     const int h_kv = h / (p.heads / p.kv_heads);
-    const int m0[2] = {(mb * kQTiles) * kBlockM, (mb * kQTiles + 1) * kBlockM};
-    const int ntiles[2] = {TilesFor(p, m0[0]), TilesFor(p, m0[1])};
+    const int m0[2] = {(mb * QT) * kBlockM, (mb * QT + 1) * kBlockM};
+    const int ntiles[2] = {TilesFor<BN>(p, m0[0]), QT > 1 ? TilesFor<BN>(p, m0[1]) : 0};
     const int n_max = max(ntiles[0], ntiles[1]);
 
     if (threadIdx.x == 0) {
@@ -149,11 +154,11 @@ flash_fwd_sm100_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
             PrefetchTensorMap(&map_q);
             PrefetchTensorMap(&map_k);
             PrefetchTensorMap(&map_v);
-            for (int t = 0; t < kQTiles; ++t) {
+            for (int t = 0; t < QT; ++t) {
                 if (ntiles[t] == 0) continue;
-                MbarExpectTx(bar(kQFull + t), G::kTileBytes);
+                MbarExpectTx(bar(kQFull + t), G::kQTileBytes);
                 for (int kb = 0; kb < G::kKBlocks; ++kb) {
-                    TmaLoad4D(q_smem + t * G::kTileBytes + kb * G::kBlockBytes, &map_q, bar(kQFull + t), kb * 64,
+                    TmaLoad4D(q_smem + t * G::kQTileBytes + kb * G::kQBlockBytes, &map_q, bar(kQFull + t), kb * 64,
                               m0[t], h, b);
                 }
             }
@@ -165,11 +170,11 @@ flash_fwd_sm100_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
                     failed = true;
                     break;
                 }
-                MbarExpectTx(bar(kKvFull + slot), G::kTileBytes);
+                MbarExpectTx(bar(kKvFull + slot), G::kKvTileBytes);
                 const CUtensorMap* map = (it & 1) ? &map_v : &map_k;
-                const int row0 = (it >> 1) * kBlockN;
+                const int row0 = (it >> 1) * BN;
                 for (int kb = 0; kb < G::kKBlocks; ++kb) {
-                    TmaLoad4D(ring_smem + slot * G::kTileBytes + kb * G::kBlockBytes, map, bar(kKvFull + slot),
+                    TmaLoad4D(ring_smem + slot * G::kKvTileBytes + kb * G::kKvBlockBytes, map, bar(kKvFull + slot),
                               kb * 64, row0, h_kv, b);
                 }
                 if (++slot == G::kSlots) {
@@ -182,24 +187,25 @@ flash_fwd_sm100_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
         // ================================ MMA issuer ================================================
         if (lane == 0) {
             constexpr uint32_t fmt = std::is_same<T, __half>::value ? kFmtF16 : kFmtBf16;
-            constexpr uint32_t idesc_s = MakeInstrDesc(fmt, 0, 0, kBlockM, kBlockN);  // Q K^T: both K-major
-            constexpr uint32_t idesc_o = MakeInstrDesc(fmt, 0, 1, kBlockM, DP);       // P V: V is MN-major
+            constexpr uint32_t idesc_s = MakeInstrDesc(fmt, 0, 0, kBlockM, BN);  // Q K^T: both K-major
+            constexpr uint32_t idesc_o = MakeInstrDesc(fmt, 0, 1, kBlockM, DP);  // P V: V is MN-major
             auto issue_s = [&](int t, int slot) {
-                const uint32_t a0 = q_smem + t * G::kTileBytes;
-                const uint32_t b0 = ring_smem + slot * G::kTileBytes;
+                const uint32_t a0 = q_smem + t * G::kQTileBytes;
+                const uint32_t b0 = ring_smem + slot * G::kKvTileBytes;
 #pragma unroll
                 for (int ks = 0; ks < DP / 16; ++ks) {
-                    const uint32_t off = (ks >> 2) * G::kBlockBytes + (ks & 3) * 32;
-                    MmaSS(tmem_base + G::kSCol + t * kBlockN, MakeSmemDesc(a0 + off, 16, 1024),
-                          MakeSmemDesc(b0 + off, 16, 1024), idesc_s, ks > 0 ? 1u : 0u);
+                    MmaSS(tmem_base + G::kSCol + t * 128,
+                          MakeSmemDesc(a0 + (ks >> 2) * G::kQBlockBytes + (ks & 3) * 32, 16, 1024),
+                          MakeSmemDesc(b0 + (ks >> 2) * G::kKvBlockBytes + (ks & 3) * 32, 16, 1024), idesc_s,
+                          ks > 0 ? 1u : 0u);
                 }
             };
             auto issue_pv = [&](int t, int slot, bool first) {
-                const uint32_t b0 = ring_smem + slot * G::kTileBytes;
+                const uint32_t b0 = ring_smem + slot * G::kKvTileBytes;
 #pragma unroll
-                for (int ks = 0; ks < kBlockN / 16; ++ks) {
-                    MmaTS(tmem_base + G::kOCol + t * DP, tmem_base + G::kSCol + t * kBlockN + ks * 8,
-                          MakeSmemDesc(b0 + ks * 2048, G::kBlockBytes, 1024), idesc_o, (!first || ks > 0) ? 1u : 0u);
+                for (int ks = 0; ks < BN / 16; ++ks) {
+                    MmaTS(tmem_base + G::kOCol + t * DP, tmem_base + G::kSCol + t * 128 + ks * 8,
+                          MakeSmemDesc(b0 + ks * 2048, G::kKvBlockBytes, 1024), idesc_o, (!first || ks > 0) ? 1u : 0u);
                 }
             };
             // ring position of load number `it` (K_j = 2j, V_j = 2j + 1)
@@ -207,14 +213,14 @@ flash_fwd_sm100_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
             auto phase_of = [&](int it) { return static_cast<uint32_t>((it / G::kSlots) & 1); };
 
             bool ok = true;
-            for (int t = 0; t < kQTiles && ok; ++t) {
+            for (int t = 0; t < QT && ok; ++t) {
                 if (ntiles[t] > 0) ok = MbarWait(bar(kQFull + t), 0, abort_flag);
             }
             if (ok && n_max > 0) {
                 ok = MbarWait(bar(kKvFull + slot_of(0)), phase_of(0), abort_flag);
                 if (ok) {
                     TcFenceAfter();
-                    for (int t = 0; t < kQTiles; ++t) {
+                    for (int t = 0; t < QT; ++t) {
                         if (ntiles[t] > 0) {
                             issue_s(t, slot_of(0));
                             MmaCommit(bar(kSFull + t));
@@ -229,7 +235,7 @@ flash_fwd_sm100_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
                 ok = MbarWait(bar(kKvFull + slot_of(it_v)), phase_of(it_v), abort_flag);
                 if (ok && j + 1 < n_max) ok = MbarWait(bar(kKvFull + slot_of(it_k)), phase_of(it_k), abort_flag);
                 if (!ok) break;
-                for (int t = 0; t < kQTiles; ++t) {
+                for (int t = 0; t < QT; ++t) {
                     if (j >= ntiles[t]) continue;
                     ok = MbarWait(bar(kPFull + t), static_cast<uint32_t>(j & 1), abort_flag);
                     if (!ok) break;
@@ -254,9 +260,9 @@ flash_fwd_sm100_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
         const int row_in_tile = quad * 32 + lane;
         const int row = m0[t] + row_in_tile;
         const uint32_t lane_bits = static_cast<uint32_t>(quad * 32) << 16;
-        const uint32_t s_addr = tmem_base + lane_bits + G::kSCol + t * kBlockN;
+        const uint32_t s_addr = tmem_base + lane_bits + G::kSCol + t * 128;
         const uint32_t o_addr = tmem_base + lane_bits + G::kOCol + t * DP;
-        const int n_t = ntiles[t];
+        const int n_t = t < QT ? ntiles[t] : 0;
 
         float m_ref = -CUDART_INF_F;  // reference point of the exponentials (log2 domain)
         float l_sum = 0.0f;
@@ -266,9 +272,9 @@ flash_fwd_sm100_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
             ok = __all_sync(0xffffffffu, MbarWait(bar(kSFull + t), static_cast<uint32_t>(j & 1), abort_flag));
             if (!ok) break;
             TcFenceAfter();
-            float s[kBlockN];
+            float s[BN];
 #pragma unroll
-            for (int cblk = 0; cblk < kBlockN / 32; ++cblk) {
+            for (int cblk = 0; cblk < BN / 32; ++cblk) {
                 uint32_t r[32];
                 TmemLd32(s_addr + cblk * 32, r);
 #pragma unroll
@@ -276,25 +282,25 @@ flash_fwd_sm100_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
             }
             TmemWaitLd();
             if (p.debug_s != nullptr && j == 0) {
-                float* dst = p.debug_s + ((static_cast<size_t>(blockIdx.x) * 2 + t) * kBlockM + row_in_tile) * kBlockN;
+                float* dst = p.debug_s + ((static_cast<size_t>(blockIdx.x) * 2 + t) * kBlockM + row_in_tile) * 128;
 #pragma unroll
-                for (int i = 0; i < kBlockN; ++i) dst[i] = s[i];
+                for (int i = 0; i < BN; ++i) dst[i] = s[i];
             }
             // scale into the log2 domain and mask
-            const int col0 = j * kBlockN;
-            const int kv_limit = p.seq_kv - col0;                                // columns >= kv_limit do not exist
-            const int causal_limit = p.causal ? (row + p.diagonal - col0 + 1) : kBlockN;  // columns >= limit are masked
+            const int col0 = j * BN;
+            const int kv_limit = p.seq_kv - col0;                                   // columns >= kv_limit do not exist
+            const int causal_limit = p.causal ? (row + p.diagonal - col0 + 1) : BN;  // columns >= limit are masked
             const int limit = min(kv_limit, causal_limit);
             float mx = -CUDART_INF_F;
-            if (limit >= kBlockN) {
+            if (limit >= BN) {
 #pragma unroll
-                for (int i = 0; i < kBlockN; ++i) {
+                for (int i = 0; i < BN; ++i) {
                     s[i] *= p.scale_log2;
                     mx = fmaxf(mx, s[i]);
                 }
             } else {
 #pragma unroll
-                for (int i = 0; i < kBlockN; ++i) {
+                for (int i = 0; i < BN; ++i) {
                     s[i] = (i < limit) ? s[i] * p.scale_log2 : -CUDART_INF_F;
                     mx = fmaxf(mx, s[i]);
                 }
@@ -322,14 +328,14 @@ flash_fwd_sm100_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
             const float m_eff = (m_ref == -CUDART_INF_F) ? 0.0f : m_ref;
             float part = 0.0f;
 #pragma unroll
-            for (int i = 0; i < kBlockN; ++i) {
+            for (int i = 0; i < BN; ++i) {
                 s[i] = Exp2(s[i] - m_eff);
                 part += s[i];
             }
             l_sum += part;
-            // P (16-bit pairs) over the first 64 columns of S_t
+            // P (16-bit pairs) over the first BN / 2 columns of S_t
 #pragma unroll
-            for (int cblk = 0; cblk < kBlockN / 64; ++cblk) {
+            for (int cblk = 0; cblk < BN / 64; ++cblk) {
                 uint32_t r[32];
 #pragma unroll
                 for (int i = 0; i < 32; ++i) r[i] = Pack2<T>(s[cblk * 64 + 2 * i], s[cblk * 64 + 2 * i + 1]);
@@ -406,17 +412,17 @@ EncodeTiledFn GetEncodeTiled() {
     return fn;
 }
 
-// [batch][heads][seq][D] through element strides (sb, sh, ss); box = 64 x 128 elements, 128B swizzle,
+// [batch][heads][seq][D] through element strides (sb, sh, ss); box = 64 elements x box_rows rows, 128B swizzle,
 // out-of-range elements read as zero.
 int MakeMap(CUtensorMap* map, const void* base, int dtype_id, int64_t d, int64_t seq, int64_t heads, int64_t batch,
-            int64_t ss, int64_t sh, int64_t sb, const char* what) {
+            int64_t ss, int64_t sh, int64_t sb, int box_rows, const char* what) {
     EncodeTiledFn encode = GetEncodeTiled();
     if (encode == nullptr) return Fail(SCA_CUDA_ERROR, "flash attention: cuTensorMapEncodeTiled is unavailable");
     const cuuint64_t dims[4] = {static_cast<cuuint64_t>(d), static_cast<cuuint64_t>(seq),
                                 static_cast<cuuint64_t>(heads), static_cast<cuuint64_t>(batch)};
     const cuuint64_t strides[3] = {static_cast<cuuint64_t>(ss) * 2, static_cast<cuuint64_t>(sh) * 2,
                                    static_cast<cuuint64_t>(sb) * 2};
-    const cuuint32_t box[4] = {64, 128, 1, 1};
+    const cuuint32_t box[4] = {64, static_cast<cuuint32_t>(box_rows), 1, 1};
     const cuuint32_t elem[4] = {1, 1, 1, 1};
     const CUtensorMapDataType type =
         dtype_id == SCA_DTYPE_F16 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT16 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16;
@@ -453,13 +459,13 @@ int* ErrorWordDevicePtr(int** host_view) {
     return dev;
 }
 
-template <typename T, int DP>
+template <typename T, int DP, int QT, int BN>
 int LaunchFlash(const ScaFlashFwdParams& f, float* debug_s, cudaStream_t stream) {
-    using G = FlashGeom<DP>;
+    using G = FlashGeom<DP, QT, BN>;
     CUtensorMap map_q, map_k, map_v;
-    if (int rc = MakeMap(&map_q, f.q, f.dtype_id, f.head_dim, f.seq_q, f.num_heads, f.batch, f.q_ss, f.q_sh, f.q_sb, "q")) return rc;
-    if (int rc = MakeMap(&map_k, f.k, f.dtype_id, f.head_dim, f.seq_kv, f.num_kv_heads, f.batch, f.k_ss, f.k_sh, f.k_sb, "k")) return rc;
-    if (int rc = MakeMap(&map_v, f.v, f.dtype_id, f.head_dim, f.seq_kv, f.num_kv_heads, f.batch, f.v_ss, f.v_sh, f.v_sb, "v")) return rc;
+    if (int rc = MakeMap(&map_q, f.q, f.dtype_id, f.head_dim, f.seq_q, f.num_heads, f.batch, f.q_ss, f.q_sh, f.q_sb, kBlockM, "q")) return rc;
+    if (int rc = MakeMap(&map_k, f.k, f.dtype_id, f.head_dim, f.seq_kv, f.num_kv_heads, f.batch, f.k_ss, f.k_sh, f.k_sb, BN, "k")) return rc;
+    if (int rc = MakeMap(&map_v, f.v, f.dtype_id, f.head_dim, f.seq_kv, f.num_kv_heads, f.batch, f.v_ss, f.v_sh, f.v_sb, BN, "v")) return rc;
 
     FlashKernelParams p{};
     p.out = f.out;
@@ -485,14 +491,14 @@ int LaunchFlash(const ScaFlashFwdParams& f, float* debug_s, cudaStream_t stream)
     p.scale_log2 = f.scale * kLog2e;
     p.causal = f.causal ? 1 : 0;
     p.diagonal = static_cast<int>(f.causal ? f.diagonal : 0);
-    p.m_blocks = static_cast<int>((f.seq_q + kQTiles * kBlockM - 1) / (kQTiles * kBlockM));
+    p.m_blocks = static_cast<int>((f.seq_q + QT * kBlockM - 1) / (QT * kBlockM));
     const int64_t ctas = static_cast<int64_t>(p.m_blocks) * p.batch * p.heads;
     if (ctas <= 0 || ctas > 0x7fffffffLL) {
         return Fail(SCA_INVALID_ARGUMENT, "flash attention: grid of " + std::to_string(ctas) + " blocks is out of range");
     }
-    const void* fn = reinterpret_cast<const void*>(&flash_fwd_sm100_kernel<T, DP>);
+    const void* fn = reinterpret_cast<const void*>(&flash_fwd_sm100_kernel<T, DP, QT, BN>);
     if (int rc = EnsureDynamicSmem(fn, G::kSmemBytes, "flash_fwd_sm100_kernel")) return rc;
-    flash_fwd_sm100_kernel<T, DP><<<static_cast<unsigned>(ctas), kFlashThreads, G::kSmemBytes, stream>>>(map_q, map_k, map_v, p);
+    flash_fwd_sm100_kernel<T, DP, QT, BN><<<static_cast<unsigned>(ctas), kFlashThreads, G::kSmemBytes, stream>>>(map_q, map_k, map_v, p);
     return CheckLaunch("flash_fwd_sm100_kernel", stream);
 }
 
@@ -527,9 +533,12 @@ int LaunchFlashTyped(const ScaFlashFwdParams& f, float* debug_s, cudaStream_t st
     // zero-fills the missing columns of Q, K and V, which leaves S and the real columns of O unchanged
     switch (f.head_dim) {
         case 32:
-        case 64: return LaunchFlash<T, 64>(f, debug_s, stream);
+        case 64: return LaunchFlash<T, 64, 2, 128>(f, debug_s, stream);
         case 96:
-        case 128: return LaunchFlash<T, 128>(f, debug_s, stream);
+        case 128: return LaunchFlash<T, 128, 2, 128>(f, debug_s, stream);
+        case 160:
+        case 192:
+        case 256: return LaunchFlash<T, 256, 1, 64>(f, debug_s, stream);
         default: break;
     }
     return Fail(SCA_INVALID_ARGUMENT, "flash attention: head_dim=" + std::to_string(f.head_dim) + " is not instantiated");
