@@ -272,39 +272,47 @@ flash_fwd_sm100_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
             ok = __all_sync(0xffffffffu, MbarWait(bar(kSFull + t), static_cast<uint32_t>(j & 1), abort_flag));
             if (!ok) break;
             TcFenceAfter();
-            float s[BN];
-#pragma unroll
-            for (int cblk = 0; cblk < BN / 32; ++cblk) {
-                uint32_t r[32];
-                TmemLd32(s_addr + cblk * 32, r);
-#pragma unroll
-                for (int i = 0; i < 32; ++i) s[cblk * 32 + i] = __uint_as_float(r[i]);
-            }
-            TmemWaitLd();
-            if (p.debug_s != nullptr && j == 0) {
-                float* dst = p.debug_s + ((static_cast<size_t>(blockIdx.x) * 2 + t) * kBlockM + row_in_tile) * 128;
-#pragma unroll
-                for (int i = 0; i < BN; ++i) dst[i] = s[i];
-            }
-            // scale into the log2 domain and mask
+            // Two passes over the S row, 64 columns at a time, so that a thread never holds more than 64
+            // scores: pass 1 finds the row max, pass 2 re-reads S, exponentiates and writes P. P (16-bit
+            // pairs) lands on the first BN / 2 columns of S_t; the half-row written in step h only covers
+            // columns that step h has already consumed.
             const int col0 = j * BN;
             const int kv_limit = p.seq_kv - col0;                                   // columns >= kv_limit do not exist
             const int causal_limit = p.causal ? (row + p.diagonal - col0 + 1) : BN;  // columns >= limit are masked
             const int limit = min(kv_limit, causal_limit);
-            float mx = -CUDART_INF_F;
-            if (limit >= BN) {
+            const bool ragged = limit < BN;
+
+            float mx4[4] = {-CUDART_INF_F, -CUDART_INF_F, -CUDART_INF_F, -CUDART_INF_F};
 #pragma unroll
-                for (int i = 0; i < BN; ++i) {
-                    s[i] *= p.scale_log2;
-                    mx = fmaxf(mx, s[i]);
+            for (int half = 0; half < BN / 64; ++half) {
+                uint32_t ra[32], rb[32];
+                TmemLd32(s_addr + half * 64, ra);
+                TmemLd32(s_addr + half * 64 + 32, rb);
+                TmemWaitLd();
+                if (p.debug_s != nullptr && j == 0) {
+                    float* dst = p.debug_s + ((static_cast<size_t>(blockIdx.x) * 2 + t) * kBlockM + row_in_tile) * 128 + half * 64;
+#pragma unroll
+                    for (int i = 0; i < 32; ++i) {
+                        dst[i] = __uint_as_float(ra[i]);
+                        dst[32 + i] = __uint_as_float(rb[i]);
+                    }
                 }
-            } else {
+                if (ragged) {
 #pragma unroll
-                for (int i = 0; i < BN; ++i) {
-                    s[i] = (i < limit) ? s[i] * p.scale_log2 : -CUDART_INF_F;
-                    mx = fmaxf(mx, s[i]);
+                    for (int i = 0; i < 32; ++i) {
+                        if (half * 64 + i >= limit) ra[i] = 0xff800000u;       // -inf
+                        if (half * 64 + 32 + i >= limit) rb[i] = 0xff800000u;
+                    }
+                }
+#pragma unroll
+                for (int i = 0; i < 32; i += 4) {
+#pragma unroll
+                    for (int e = 0; e < 4; ++e) {
+                        mx4[e] = fmaxf(mx4[e], fmaxf(__uint_as_float(ra[i + e]), __uint_as_float(rb[i + e])));
+                    }
                 }
             }
+            const float mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3])) * p.scale_log2;  // scale > 0
             const float m_new = fmaxf(m_ref, mx);
             // Move the reference point only when it is far off; O and l are rescaled to match.
             const bool move = (j == 0) || (m_new - m_ref > kRescaleThreshold);
@@ -325,22 +333,38 @@ flash_fwd_sm100_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
                 l_sum *= alpha;
             }
             if (move) m_ref = m_new;
-            const float m_eff = (m_ref == -CUDART_INF_F) ? 0.0f : m_ref;
-            float part = 0.0f;
+            const float neg_m = (m_ref == -CUDART_INF_F) ? 0.0f : -m_ref;
+            float part4[4] = {0.0f, 0.0f, 0.0f, 0.0f};
 #pragma unroll
-            for (int i = 0; i < BN; ++i) {
-                s[i] = Exp2(s[i] - m_eff);
-                part += s[i];
+            for (int half = 0; half < BN / 64; ++half) {
+                uint32_t ra[32], rb[32];
+                TmemLd32(s_addr + half * 64, ra);
+                TmemLd32(s_addr + half * 64 + 32, rb);
+                TmemWaitLd();
+                if (ragged) {
+#pragma unroll
+                    for (int i = 0; i < 32; ++i) {
+                        if (half * 64 + i >= limit) ra[i] = 0xff800000u;
+                        if (half * 64 + 32 + i >= limit) rb[i] = 0xff800000u;
+                    }
+                }
+                uint32_t pk[32];
+#pragma unroll
+                for (int i = 0; i < 32; i += 2) {
+                    const float a0 = Exp2(fmaf(__uint_as_float(ra[i]), p.scale_log2, neg_m));
+                    const float a1 = Exp2(fmaf(__uint_as_float(ra[i + 1]), p.scale_log2, neg_m));
+                    const float b0 = Exp2(fmaf(__uint_as_float(rb[i]), p.scale_log2, neg_m));
+                    const float b1 = Exp2(fmaf(__uint_as_float(rb[i + 1]), p.scale_log2, neg_m));
+                    part4[0] += a0;
+                    part4[1] += a1;
+                    part4[2] += b0;
+                    part4[3] += b1;
+                    pk[i / 2] = Pack2<T>(a0, a1);
+                    pk[16 + i / 2] = Pack2<T>(b0, b1);
+                }
+                TmemSt32(s_addr + half * 32, pk);
             }
-            l_sum += part;
-            // P (16-bit pairs) over the first BN / 2 columns of S_t
-#pragma unroll
-            for (int cblk = 0; cblk < BN / 64; ++cblk) {
-                uint32_t r[32];
-#pragma unroll
-                for (int i = 0; i < 32; ++i) r[i] = Pack2<T>(s[cblk * 64 + 2 * i], s[cblk * 64 + 2 * i + 1]);
-                TmemSt32(s_addr + cblk * 32, r);
-            }
+            l_sum += (part4[0] + part4[1]) + (part4[2] + part4[3]);
             TmemWaitSt();
             TcFenceBefore();
             MbarArrive(bar(kPFull + t));
