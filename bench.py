@@ -52,7 +52,7 @@ def measured_peaks():
 # clocks during the timed region (read-only NVML queries)
 # --------------------------------------------------------------------------------------------------
 class ClockSampler:
-    def __init__(self, index: int, period_s: float = 0.005):
+    def __init__(self, index: int, period_s: float = 0.001):
         self.index, self.period = index, period_s
         self.samples, self.reasons, self.max_mhz = [], set(), None
         self._stop = threading.Event()
@@ -371,6 +371,9 @@ def main():
     ap.add_argument("--workload", default=DEFAULT_WORKLOAD, choices=sorted(WORKLOADS))
     ap.add_argument("--e2e-steps", type=int, default=0, help="0 = min(steps, 5)")
     ap.add_argument("--seed", type=int, default=0)
+    ap.add_argument("--capture", action="store_true",
+                    help="profiler-sized variant of the workload (same kernels, a few hundred MB): flash B=1, "
+                         "decode B=16, paged 32 sequences in a 20k-block pool; skips the e2e and CPU legs")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3)
 
@@ -392,6 +395,14 @@ def main():
         dist.init_process_group("nccl", device_id=device)
 
     wl = WORKLOADS[args.workload]()
+    if args.capture:
+        if isinstance(wl, FlashWorkload):
+            wl.B = 1
+        elif isinstance(wl, DecodeWorkload):
+            wl.B = 16
+        else:
+            wl.NSEQ, wl.NBLK = 32, 20000
+        wl.name += "_capture"
     wl.setup(torch, device, args.seed + rank)
     stream = torch.cuda.current_stream()
 
@@ -416,35 +427,38 @@ def main():
 
     # end to end through the public operator with host buffers: pinned H2D of the step's inputs,
     # the step, D2H of its result - all inside the timed region
-    wl.e2e_setup(torch)
     e2e_steps = args.e2e_steps or min(args.steps, 5)
-    wl.e2e_step()
-    barrier()
-    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    e0.record(stream)
-    for _ in range(e2e_steps):
+    e2e_ms = None
+    wl.h2d = wl.d2h = 0
+    if not args.capture:
+        wl.e2e_setup(torch)
         wl.e2e_step()
-    e1.record(stream)
-    barrier()
-    e2e_ms = e0.elapsed_time(e1) / e2e_steps
+        barrier()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record(stream)
+        for _ in range(e2e_steps):
+            wl.e2e_step()
+        e1.record(stream)
+        barrier()
+        e2e_ms = e0.elapsed_time(e1) / e2e_steps
 
     if world > 1:
-        t = torch.tensor([ms_total, e2e_ms], device=device, dtype=torch.float64)
+        t = torch.tensor([ms_total, e2e_ms or 0.0], device=device, dtype=torch.float64)
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
-        ms_total, e2e_ms = float(t[0]), float(t[1])
+        ms_total, e2e_ms = float(t[0]), (float(t[1]) if e2e_ms is not None else None)
     ms_step = ms_total / args.steps
     work = wl.work_per_step()
     scale = 1e9 if wl.unit == "GB/s" else 1e12
     per_gpu = work / (ms_step * 1e-3) / scale
     value = per_gpu * world
-    e2e_value = work / (e2e_ms * 1e-3) / scale * world
+    e2e_value = work / (e2e_ms * 1e-3) / scale * world if e2e_ms else None
 
     if rank == 0:
         peaks = measured_peaks()
         peak = peaks["hbm_gbs"] if wl.bound == "hbm" else peaks["tflops"]
         nominal = NOMINAL_HBM_GBS if wl.bound == "hbm" else NOMINAL_TENSOR_TFLOPS
         cpu = None
-        if world == 1 or True:
+        if not args.capture:
             cw, cs, desc, kind = wl.cpu_sample(threads, "port")
             cpu = {"value": cw / cs / scale, "unit": wl.unit, "cores": threads, "kind": kind,
                    "sample": desc + f" ({cs:.1f} s of FP64 host work)"}

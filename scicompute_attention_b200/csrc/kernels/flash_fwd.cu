@@ -26,6 +26,7 @@
 // FLOPs per (query, key) pair that is visible: 4 * D. Algorithmic HBM bytes: Q + K + V + O once.
 #include <cuda.h>
 
+#include <algorithm>
 #include <mutex>
 #include <type_traits>
 
@@ -104,7 +105,9 @@ flash_fwd_sm100_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
     constexpr int kSFull = kKvEmpty + G::kSlots;    // [2]
     constexpr int kPFull = kSFull + 2;              // [2]
     constexpr int kODone = kPFull + 2;              // [2]
-    constexpr int kNumBars = kODone + 2;
+    constexpr int kQEmpty = kODone + 2;             // [2]
+    constexpr int kOFree = kQEmpty + 2;             // [2]
+    constexpr int kNumBars = kOFree + 2;
     static_assert(kNumBars * 8 + 16 <= G::kBarrierBytes, "barrier area too small");
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(smem + (bar_base - smem_base) + kNumBars * 8);
     volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
@@ -112,27 +115,43 @@ flash_fwd_sm100_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
     const int warp = threadIdx.x >> 5;
     const int lane = threadIdx.x & 31;
 
-    // ---- which work does this CTA own (heaviest causal tiles first) --------------------------------
+    // ---- work items: (query block, batch*head), heaviest causal blocks first; a CTA walks the list with
+    // stride gridDim.x so that the loads of its next item overlap the tail of the current one ----------
     const int bh_count = p.batch * p.heads;
-    const int mb = p.m_blocks - 1 - static_cast<int>(blockIdx.x) / bh_count;
-    const int bh = static_cast<int>(blockIdx.x) % bh_count;
-    const int b = bh / p.heads;
-    const int h = bh % p.heads;
-    const int h_kv = h / (p.heads / p.kv_heads);
-    const int m0[2] = {(mb * QT) * kBlockM, (mb * QT + 1) * kBlockM};
-    const int ntiles[2] = {TilesFor<BN>(p, m0[0]), QT > 1 ? TilesFor<BN>(p, m0[1]) : 0};
-    const int n_max = max(ntiles[0], ntiles[1]);
+    const int total_items = p.m_blocks * bh_count;
+    struct Item {
+        int b, h, h_kv;
+        int m0[2];
+        int ntiles[2];
+        int n_max;
+    };
+    auto decode_item = [&](int idx) {
+        Item w;
+        const int mb = p.m_blocks - 1 - idx / bh_count;
+        const int bh = idx % bh_count;
+        w.b = bh / p.heads;
+        w.h = bh % p.heads;
+        w.h_kv = w.h / (p.heads / p.kv_heads);
+        w.m0[0] = (mb * QT) * kBlockM;
+        w.m0[1] = (mb * QT + 1) * kBlockM;
+        w.ntiles[0] = TilesFor<BN>(p, w.m0[0]);
+        w.ntiles[1] = QT > 1 ? TilesFor<BN>(p, w.m0[1]) : 0;
+        w.n_max = max(w.ntiles[0], w.ntiles[1]);
+        return w;
+    };
 
     if (threadIdx.x == 0) {
-        for (int i = 0; i < 2; ++i) MbarInit(bar(kQFull + i), 1);
-        for (int i = 0; i < G::kSlots; ++i) {
-            MbarInit(bar(kKvFull + i), 1);
-            MbarInit(bar(kKvEmpty + i), 1);
-        }
         for (int i = 0; i < 2; ++i) {
+            MbarInit(bar(kQFull + i), 1);
+            MbarInit(bar(kQEmpty + i), 1);
             MbarInit(bar(kSFull + i), 1);
             MbarInit(bar(kPFull + i), 128);
             MbarInit(bar(kODone + i), 1);
+            MbarInit(bar(kOFree + i), 128);
+        }
+        for (int i = 0; i < G::kSlots; ++i) {
+            MbarInit(bar(kKvFull + i), 1);
+            MbarInit(bar(kKvEmpty + i), 1);
         }
         *abort_flag = 0;
         FenceBarrierInit();
@@ -154,34 +173,37 @@ flash_fwd_sm100_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
             PrefetchTensorMap(&map_q);
             PrefetchTensorMap(&map_k);
             PrefetchTensorMap(&map_v);
-            for (int t = 0; t < QT; ++t) {
-                if (ntiles[t] == 0) continue;
-                MbarExpectTx(bar(kQFull + t), G::kQTileBytes);
-                for (int kb = 0; kb < G::kKBlocks; ++kb) {
-                    TmaLoad4D(q_smem + t * G::kQTileBytes + kb * G::kQBlockBytes, &map_q, bar(kQFull + t), kb * 64,
-                              m0[t], h, b);
+            uint32_t q_uses[2] = {0, 0};   // how often each query buffer has been filled so far
+            uint32_t kv_loads = 0;         // K/V tiles loaded so far (ring position)
+            bool ok = true;
+            for (int idx = blockIdx.x; idx < total_items && ok; idx += gridDim.x) {
+                const Item w = decode_item(idx);
+                for (int t = 0; t < QT && ok; ++t) {
+                    if (w.ntiles[t] == 0) continue;
+                    // the previous item's last S = Q K^T must have read the buffer
+                    if (q_uses[t] > 0) ok = MbarWait(bar(kQEmpty + t), (q_uses[t] - 1) & 1u, abort_flag);
+                    if (!ok) break;
+                    MbarExpectTx(bar(kQFull + t), G::kQTileBytes);
+                    for (int kb = 0; kb < G::kKBlocks; ++kb) {
+                        TmaLoad4D(q_smem + t * G::kQTileBytes + kb * G::kQBlockBytes, &map_q, bar(kQFull + t), kb * 64,
+                                  w.m0[t], w.h, w.b);
+                    }
+                    ++q_uses[t];
+                }
+                for (int it = 0; it < 2 * w.n_max && ok; ++it, ++kv_loads) {  // K_0, V_0, K_1, V_1, ...
+                    const uint32_t slot = kv_loads % G::kSlots;
+                    const uint32_t phase = (kv_loads / G::kSlots) & 1u;
+                    ok = MbarWait(bar(kKvEmpty + slot), phase ^ 1u, abort_flag);
+                    if (!ok) break;
+                    MbarExpectTx(bar(kKvFull + slot), G::kKvTileBytes);
+                    const CUtensorMap* map = (it & 1) ? &map_v : &map_k;
+                    for (int kb = 0; kb < G::kKBlocks; ++kb) {
+                        TmaLoad4D(ring_smem + slot * G::kKvTileBytes + kb * G::kKvBlockBytes, map, bar(kKvFull + slot),
+                                  kb * 64, (it >> 1) * BN, w.h_kv, w.b);
+                    }
                 }
             }
-            const int loads = 2 * n_max;  // K_0, V_0, K_1, V_1, ...
-            int slot = 0;
-            uint32_t phase = 0;
-            for (int it = 0; it < loads; ++it) {
-                if (!MbarWait(bar(kKvEmpty + slot), phase ^ 1u, abort_flag)) {
-                    failed = true;
-                    break;
-                }
-                MbarExpectTx(bar(kKvFull + slot), G::kKvTileBytes);
-                const CUtensorMap* map = (it & 1) ? &map_v : &map_k;
-                const int row0 = (it >> 1) * BN;
-                for (int kb = 0; kb < G::kKBlocks; ++kb) {
-                    TmaLoad4D(ring_smem + slot * G::kKvTileBytes + kb * G::kKvBlockBytes, map, bar(kKvFull + slot),
-                              kb * 64, row0, h_kv, b);
-                }
-                if (++slot == G::kSlots) {
-                    slot = 0;
-                    phase ^= 1u;
-                }
-            }
+            failed = !ok;
         }
     } else if (warp == 1) {
         // ================================ MMA issuer ================================================
@@ -189,67 +211,88 @@ flash_fwd_sm100_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
             constexpr uint32_t fmt = std::is_same<T, __half>::value ? kFmtF16 : kFmtBf16;
             constexpr uint32_t idesc_s = MakeInstrDesc(fmt, 0, 0, kBlockM, BN);  // Q K^T: both K-major
             constexpr uint32_t idesc_o = MakeInstrDesc(fmt, 0, 1, kBlockM, DP);  // P V: V is MN-major
-            auto issue_s = [&](int t, int slot) {
-                const uint32_t a0 = q_smem + t * G::kQTileBytes;
-                const uint32_t b0 = ring_smem + slot * G::kKvTileBytes;
+            // Descriptors are built once and advanced by compile-time constants, so that issuing one
+            // tcgen05.mma costs a handful of instructions (this thread alone has to keep the tensor pipe fed).
+            const uint64_t kmajor_hi = MakeSmemDesc(0, 16, 1024);                 // K-major operands (Q and K)
+            const uint64_t vmajor_hi = MakeSmemDesc(0, G::kKvBlockBytes, 1024);   // MN-major operand (V)
+            const uint64_t q_desc[2] = {kmajor_hi | (q_smem >> 4), kmajor_hi | ((q_smem + G::kQTileBytes) >> 4)};
+            const uint32_t s_tmem[2] = {tmem_base + G::kSCol, tmem_base + G::kSCol + 128};
+            const uint32_t o_tmem[2] = {tmem_base + G::kOCol, tmem_base + G::kOCol + DP};
+            auto issue_s = [&](int t, uint32_t slot) {
+                const uint64_t a0 = q_desc[t];
+                const uint64_t b0 = kmajor_hi | ((ring_smem + slot * G::kKvTileBytes) >> 4);
 #pragma unroll
                 for (int ks = 0; ks < DP / 16; ++ks) {
-                    MmaSS(tmem_base + G::kSCol + t * 128,
-                          MakeSmemDesc(a0 + (ks >> 2) * G::kQBlockBytes + (ks & 3) * 32, 16, 1024),
-                          MakeSmemDesc(b0 + (ks >> 2) * G::kKvBlockBytes + (ks & 3) * 32, 16, 1024), idesc_s,
-                          ks > 0 ? 1u : 0u);
+                    constexpr int kStep = 32 >> 4;  // 16 elements = 32 bytes inside a 128-byte swizzle row
+                    const uint32_t qa = ((ks >> 2) * G::kQBlockBytes >> 4) + (ks & 3) * kStep;
+                    const uint32_t kb = ((ks >> 2) * G::kKvBlockBytes >> 4) + (ks & 3) * kStep;
+                    if (ks == 0) MmaSS<false>(s_tmem[t], a0 + qa, b0 + kb, idesc_s);
+                    else MmaSS<true>(s_tmem[t], a0 + qa, b0 + kb, idesc_s);
                 }
             };
-            auto issue_pv = [&](int t, int slot, bool first) {
-                const uint32_t b0 = ring_smem + slot * G::kKvTileBytes;
+            auto issue_pv = [&](int t, uint32_t slot, bool first) {
+                const uint64_t b0 = vmajor_hi | ((ring_smem + slot * G::kKvTileBytes) >> 4);
 #pragma unroll
                 for (int ks = 0; ks < BN / 16; ++ks) {
-                    MmaTS(tmem_base + G::kOCol + t * DP, tmem_base + G::kSCol + t * 128 + ks * 8,
-                          MakeSmemDesc(b0 + ks * 2048, G::kKvBlockBytes, 1024), idesc_o, (!first || ks > 0) ? 1u : 0u);
+                    // 16 keys further: 8 packed P columns in tensor memory, 16 rows (2048 bytes) of V
+                    if (ks == 0) MmaTSFlag(o_tmem[t], s_tmem[t], b0, idesc_o, first ? 0u : 1u);
+                    else MmaTS<true>(o_tmem[t], s_tmem[t] + ks * 8, b0 + ks * (2048 >> 4), idesc_o);
                 }
             };
-            // ring position of load number `it` (K_j = 2j, V_j = 2j + 1)
-            auto slot_of = [&](int it) { return it % G::kSlots; };
-            auto phase_of = [&](int it) { return static_cast<uint32_t>((it / G::kSlots) & 1); };
-
+            uint32_t q_uses[2] = {0, 0};    // items finished per query buffer
+            uint32_t steps[2] = {0, 0};     // KV tiles processed per query tile (phase of s_full / p_full / o_done)
+            uint32_t kv_base = 0;           // ring position of this item's K_0
             bool ok = true;
-            for (int t = 0; t < QT && ok; ++t) {
-                if (ntiles[t] > 0) ok = MbarWait(bar(kQFull + t), 0, abort_flag);
-            }
-            if (ok && n_max > 0) {
-                ok = MbarWait(bar(kKvFull + slot_of(0)), phase_of(0), abort_flag);
-                if (ok) {
-                    TcFenceAfter();
-                    for (int t = 0; t < QT; ++t) {
-                        if (ntiles[t] > 0) {
+            for (int idx = blockIdx.x; idx < total_items && ok; idx += gridDim.x) {
+                const Item w = decode_item(idx);
+                auto slot_of = [&](int it) { return (kv_base + it) % G::kSlots; };
+                auto phase_of = [&](int it) { return ((kv_base + it) / G::kSlots) & 1u; };
+                for (int t = 0; t < QT && ok; ++t) {
+                    if (w.ntiles[t] > 0) ok = MbarWait(bar(kQFull + t), q_uses[t] & 1u, abort_flag);
+                }
+                if (ok && w.n_max > 0) {
+                    ok = MbarWait(bar(kKvFull + slot_of(0)), phase_of(0), abort_flag);
+                    if (ok) {
+                        TcFenceAfter();
+                        for (int t = 0; t < QT; ++t) {
+                            if (w.ntiles[t] == 0) continue;
                             issue_s(t, slot_of(0));
                             MmaCommit(bar(kSFull + t));
+                            if (w.ntiles[t] == 1) MmaCommit(bar(kQEmpty + t));  // last read of this query tile
+                        }
+                        MmaCommit(bar(kKvEmpty + slot_of(0)));
+                    }
+                }
+                for (int j = 0; j < w.n_max && ok; ++j) {
+                    const int it_v = 2 * j + 1;
+                    const int it_k = 2 * j + 2;
+                    ok = MbarWait(bar(kKvFull + slot_of(it_v)), phase_of(it_v), abort_flag);
+                    if (ok && j + 1 < w.n_max) ok = MbarWait(bar(kKvFull + slot_of(it_k)), phase_of(it_k), abort_flag);
+                    if (!ok) break;
+                    for (int t = 0; t < QT; ++t) {
+                        if (j >= w.ntiles[t]) continue;
+                        ok = MbarWait(bar(kPFull + t), steps[t] & 1u, abort_flag);
+                        // the first P V of an item overwrites O: the previous item's O must have been read out
+                        if (ok && j == 0 && q_uses[t] > 0) ok = MbarWait(bar(kOFree + t), (q_uses[t] - 1) & 1u, abort_flag);
+                        if (!ok) break;
+                        TcFenceAfter();
+                        issue_pv(t, slot_of(it_v), j == 0);
+                        MmaCommit(bar(kODone + t));
+                        ++steps[t];
+                        if (j + 1 < w.ntiles[t]) {
+                            issue_s(t, slot_of(it_k));
+                            MmaCommit(bar(kSFull + t));
+                            if (j + 2 == w.ntiles[t]) MmaCommit(bar(kQEmpty + t));
                         }
                     }
-                    MmaCommit(bar(kKvEmpty + slot_of(0)));
-                }
-            }
-            for (int j = 0; j < n_max && ok; ++j) {
-                const int it_v = 2 * j + 1;
-                const int it_k = 2 * j + 2;
-                ok = MbarWait(bar(kKvFull + slot_of(it_v)), phase_of(it_v), abort_flag);
-                if (ok && j + 1 < n_max) ok = MbarWait(bar(kKvFull + slot_of(it_k)), phase_of(it_k), abort_flag);
-                if (!ok) break;
-                for (int t = 0; t < QT; ++t) {
-                    if (j >= ntiles[t]) continue;
-                    ok = MbarWait(bar(kPFull + t), static_cast<uint32_t>(j & 1), abort_flag);
                     if (!ok) break;
-                    TcFenceAfter();
-                    issue_pv(t, slot_of(it_v), j == 0);
-                    MmaCommit(bar(kODone + t));
-                    if (j + 1 < ntiles[t]) {
-                        issue_s(t, slot_of(it_k));
-                        MmaCommit(bar(kSFull + t));
-                    }
+                    MmaCommit(bar(kKvEmpty + slot_of(it_v)));
+                    if (j + 1 < w.n_max) MmaCommit(bar(kKvEmpty + slot_of(it_k)));
                 }
-                if (!ok) break;
-                MmaCommit(bar(kKvEmpty + slot_of(it_v)));
-                if (j + 1 < n_max) MmaCommit(bar(kKvEmpty + slot_of(it_k)));
+                for (int t = 0; t < QT; ++t) {
+                    if (w.ntiles[t] > 0) ++q_uses[t];
+                }
+                kv_base += 2 * w.n_max;
             }
             failed = !ok;
         }
@@ -258,149 +301,156 @@ flash_fwd_sm100_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
         const int t = (warp - 4) >> 2;
         const int quad = warp & 3;
         const int row_in_tile = quad * 32 + lane;
-        const int row = m0[t] + row_in_tile;
         const uint32_t lane_bits = static_cast<uint32_t>(quad * 32) << 16;
         const uint32_t s_addr = tmem_base + lane_bits + G::kSCol + t * 128;
         const uint32_t o_addr = tmem_base + lane_bits + G::kOCol + t * DP;
-        const int n_t = t < QT ? ntiles[t] : 0;
-
-        float m_ref = -CUDART_INF_F;  // reference point of the exponentials (log2 domain)
-        float l_sum = 0.0f;
+        uint32_t steps = 0;  // KV tiles this group has processed (phase of s_full / p_full / o_done)
         bool ok = true;
 
-        for (int j = 0; j < n_t; ++j) {
-            ok = __all_sync(0xffffffffu, MbarWait(bar(kSFull + t), static_cast<uint32_t>(j & 1), abort_flag));
-            if (!ok) break;
-            TcFenceAfter();
-            // Two passes over the S row, 64 columns at a time, so that a thread never holds more than 64
-            // scores: pass 1 finds the row max, pass 2 re-reads S, exponentiates and writes P. P (16-bit
-            // pairs) lands on the first BN / 2 columns of S_t; the half-row written in step h only covers
-            // columns that step h has already consumed.
-            const int col0 = j * BN;
-            const int kv_limit = p.seq_kv - col0;                                   // columns >= kv_limit do not exist
-            const int causal_limit = p.causal ? (row + p.diagonal - col0 + 1) : BN;  // columns >= limit are masked
-            const int limit = min(kv_limit, causal_limit);
-            const bool ragged = limit < BN;
+        for (int idx = blockIdx.x; idx < total_items && ok && t < QT; idx += gridDim.x) {
+            const Item w = decode_item(idx);
+            const int n_t = w.ntiles[t];
+            if (n_t == 0) continue;
+            const int row = w.m0[t] + row_in_tile;
+            float m_ref = -CUDART_INF_F;  // reference point of the exponentials (log2 domain)
+            float l_sum = 0.0f;
 
-            float mx4[4] = {-CUDART_INF_F, -CUDART_INF_F, -CUDART_INF_F, -CUDART_INF_F};
-#pragma unroll
-            for (int half = 0; half < BN / 64; ++half) {
-                uint32_t ra[32], rb[32];
-                TmemLd32(s_addr + half * 64, ra);
-                TmemLd32(s_addr + half * 64 + 32, rb);
-                TmemWaitLd();
-                if (p.debug_s != nullptr && j == 0) {
-                    float* dst = p.debug_s + ((static_cast<size_t>(blockIdx.x) * 2 + t) * kBlockM + row_in_tile) * 128 + half * 64;
-#pragma unroll
-                    for (int i = 0; i < 32; ++i) {
-                        dst[i] = __uint_as_float(ra[i]);
-                        dst[32 + i] = __uint_as_float(rb[i]);
-                    }
-                }
-                if (ragged) {
-#pragma unroll
-                    for (int i = 0; i < 32; ++i) {
-                        if (half * 64 + i >= limit) ra[i] = 0xff800000u;       // -inf
-                        if (half * 64 + 32 + i >= limit) rb[i] = 0xff800000u;
-                    }
-                }
-#pragma unroll
-                for (int i = 0; i < 32; i += 4) {
-#pragma unroll
-                    for (int e = 0; e < 4; ++e) {
-                        mx4[e] = fmaxf(mx4[e], fmaxf(__uint_as_float(ra[i + e]), __uint_as_float(rb[i + e])));
-                    }
-                }
-            }
-            const float mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3])) * p.scale_log2;  // scale > 0
-            const float m_new = fmaxf(m_ref, mx);
-            // Move the reference point only when it is far off; O and l are rescaled to match.
-            const bool move = (j == 0) || (m_new - m_ref > kRescaleThreshold);
-            if (j > 0 && __any_sync(0xffffffffu, move)) {
-                ok = __all_sync(0xffffffffu, MbarWait(bar(kODone + t), static_cast<uint32_t>((j - 1) & 1), abort_flag));
+            for (int j = 0; j < n_t; ++j, ++steps) {
+                ok = __all_sync(0xffffffffu, MbarWait(bar(kSFull + t), steps & 1u, abort_flag));
                 if (!ok) break;
                 TcFenceAfter();
-                const float alpha = move ? Exp2(m_ref - m_new) : 1.0f;  // m_ref = -inf -> 0
-#pragma unroll
-                for (int cblk = 0; cblk < DP / 32; ++cblk) {
-                    uint32_t r[32];
-                    TmemLd32(o_addr + cblk * 32, r);
-                    TmemWaitLd();
-#pragma unroll
-                    for (int i = 0; i < 32; ++i) r[i] = __float_as_uint(__uint_as_float(r[i]) * alpha);
-                    TmemSt32(o_addr + cblk * 32, r);
-                }
-                l_sum *= alpha;
-            }
-            if (move) m_ref = m_new;
-            const float neg_m = (m_ref == -CUDART_INF_F) ? 0.0f : -m_ref;
-            float part4[4] = {0.0f, 0.0f, 0.0f, 0.0f};
-#pragma unroll
-            for (int half = 0; half < BN / 64; ++half) {
-                uint32_t ra[32], rb[32];
-                TmemLd32(s_addr + half * 64, ra);
-                TmemLd32(s_addr + half * 64 + 32, rb);
-                TmemWaitLd();
-                if (ragged) {
-#pragma unroll
-                    for (int i = 0; i < 32; ++i) {
-                        if (half * 64 + i >= limit) ra[i] = 0xff800000u;
-                        if (half * 64 + 32 + i >= limit) rb[i] = 0xff800000u;
-                    }
-                }
-                uint32_t pk[32];
-#pragma unroll
-                for (int i = 0; i < 32; i += 2) {
-                    const float a0 = Exp2(fmaf(__uint_as_float(ra[i]), p.scale_log2, neg_m));
-                    const float a1 = Exp2(fmaf(__uint_as_float(ra[i + 1]), p.scale_log2, neg_m));
-                    const float b0 = Exp2(fmaf(__uint_as_float(rb[i]), p.scale_log2, neg_m));
-                    const float b1 = Exp2(fmaf(__uint_as_float(rb[i + 1]), p.scale_log2, neg_m));
-                    part4[0] += a0;
-                    part4[1] += a1;
-                    part4[2] += b0;
-                    part4[3] += b1;
-                    pk[i / 2] = Pack2<T>(a0, a1);
-                    pk[16 + i / 2] = Pack2<T>(b0, b1);
-                }
-                TmemSt32(s_addr + half * 32, pk);
-            }
-            l_sum += (part4[0] + part4[1]) + (part4[2] + part4[3]);
-            TmemWaitSt();
-            TcFenceBefore();
-            MbarArrive(bar(kPFull + t));
-        }
+                // Two passes over the S row, 64 columns at a time, so that a thread never holds more than 64
+                // scores: pass 1 finds the row max, pass 2 re-reads S, exponentiates and writes P. P (16-bit
+                // pairs) lands on the first BN / 2 columns of S_t; the half-row written in step h only covers
+                // columns that step h has already consumed.
+                const int col0 = j * BN;
+                const int kv_limit = p.seq_kv - col0;                                   // columns >= kv_limit do not exist
+                const int causal_limit = p.causal ? (row + p.diagonal - col0 + 1) : BN;  // columns >= limit are masked
+                const int limit = min(kv_limit, causal_limit);
+                const bool ragged = limit < BN;
 
-        // ---- epilogue: O / l -> global, optional LSE ------------------------------------------------
-        if (ok && n_t > 0) {
-            ok = __all_sync(0xffffffffu, MbarWait(bar(kODone + t), static_cast<uint32_t>((n_t - 1) & 1), abort_flag));
-            if (ok) {
-                TcFenceAfter();
-                const float inv = l_sum > 0.0f ? 1.0f / l_sum : 0.0f;
-                T* o_row = reinterpret_cast<T*>(p.out) + b * p.o_sb + h * p.o_sh + static_cast<int64_t>(row) * p.o_ss;
-#pragma unroll
-                for (int cblk = 0; cblk < DP / 32; ++cblk) {
-                    uint32_t r[32];
-                    TmemLd32(o_addr + cblk * 32, r);
+                float mx4[4] = {-CUDART_INF_F, -CUDART_INF_F, -CUDART_INF_F, -CUDART_INF_F};
+    #pragma unroll
+                for (int half = 0; half < BN / 64; ++half) {
+                    uint32_t ra[32], rb[32];
+                    TmemLd32(s_addr + half * 64, ra);
+                    TmemLd32(s_addr + half * 64 + 32, rb);
                     TmemWaitLd();
-                    if (row < p.seq_q) {
-#pragma unroll
-                        for (int v8 = 0; v8 < 4; ++v8) {
-                            const int d0 = cblk * 32 + v8 * 8;
-                            if (d0 < p.head_dim) {
-                                uint4 pk;
-                                pk.x = Pack2<T>(__uint_as_float(r[v8 * 8 + 0]) * inv, __uint_as_float(r[v8 * 8 + 1]) * inv);
-                                pk.y = Pack2<T>(__uint_as_float(r[v8 * 8 + 2]) * inv, __uint_as_float(r[v8 * 8 + 3]) * inv);
-                                pk.z = Pack2<T>(__uint_as_float(r[v8 * 8 + 4]) * inv, __uint_as_float(r[v8 * 8 + 5]) * inv);
-                                pk.w = Pack2<T>(__uint_as_float(r[v8 * 8 + 6]) * inv, __uint_as_float(r[v8 * 8 + 7]) * inv);
-                                *reinterpret_cast<uint4*>(o_row + d0) = pk;
-                            }
+                    if (p.debug_s != nullptr && j == 0) {
+                        float* dst = p.debug_s + ((static_cast<size_t>(idx) * 2 + t) * kBlockM + row_in_tile) * 128 + half * 64;
+    #pragma unroll
+                        for (int i = 0; i < 32; ++i) {
+                            dst[i] = __uint_as_float(ra[i]);
+                            dst[32 + i] = __uint_as_float(rb[i]);
+                        }
+                    }
+                    if (ragged) {
+    #pragma unroll
+                        for (int i = 0; i < 32; ++i) {
+                            if (half * 64 + i >= limit) ra[i] = 0xff800000u;       // -inf
+                            if (half * 64 + 32 + i >= limit) rb[i] = 0xff800000u;
+                        }
+                    }
+    #pragma unroll
+                    for (int i = 0; i < 32; i += 4) {
+    #pragma unroll
+                        for (int e = 0; e < 4; ++e) {
+                            mx4[e] = fmaxf(mx4[e], fmaxf(__uint_as_float(ra[i + e]), __uint_as_float(rb[i + e])));
                         }
                     }
                 }
-                if (p.lse != nullptr && row < p.seq_q) {
-                    p.lse[(static_cast<int64_t>(b) * p.heads + h) * p.seq_q + row] =
-                        l_sum > 0.0f ? (m_ref + log2f(l_sum)) * kLn2 : -CUDART_INF_F;
+                const float mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3])) * p.scale_log2;  // scale > 0
+                const float m_new = fmaxf(m_ref, mx);
+                // Move the reference point only when it is far off; O and l are rescaled to match.
+                const bool move = (j == 0) || (m_new - m_ref > kRescaleThreshold);
+                if (j > 0 && __any_sync(0xffffffffu, move)) {
+                    ok = __all_sync(0xffffffffu, MbarWait(bar(kODone + t), (steps - 1) & 1u, abort_flag));
+                    if (!ok) break;
+                    TcFenceAfter();
+                    const float alpha = move ? Exp2(m_ref - m_new) : 1.0f;  // m_ref = -inf -> 0
+    #pragma unroll
+                    for (int cblk = 0; cblk < DP / 32; ++cblk) {
+                        uint32_t r[32];
+                        TmemLd32(o_addr + cblk * 32, r);
+                        TmemWaitLd();
+    #pragma unroll
+                        for (int i = 0; i < 32; ++i) r[i] = __float_as_uint(__uint_as_float(r[i]) * alpha);
+                        TmemSt32(o_addr + cblk * 32, r);
+                    }
+                    l_sum *= alpha;
                 }
+                if (move) m_ref = m_new;
+                const float neg_m = (m_ref == -CUDART_INF_F) ? 0.0f : -m_ref;
+                float part4[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+    #pragma unroll
+                for (int half = 0; half < BN / 64; ++half) {
+                    uint32_t ra[32], rb[32];
+                    TmemLd32(s_addr + half * 64, ra);
+                    TmemLd32(s_addr + half * 64 + 32, rb);
+                    TmemWaitLd();
+                    if (ragged) {
+    #pragma unroll
+                        for (int i = 0; i < 32; ++i) {
+                            if (half * 64 + i >= limit) ra[i] = 0xff800000u;
+                            if (half * 64 + 32 + i >= limit) rb[i] = 0xff800000u;
+                        }
+                    }
+                    uint32_t pk[32];
+    #pragma unroll
+                    for (int i = 0; i < 32; i += 2) {
+                        const float a0 = Exp2(fmaf(__uint_as_float(ra[i]), p.scale_log2, neg_m));
+                        const float a1 = Exp2(fmaf(__uint_as_float(ra[i + 1]), p.scale_log2, neg_m));
+                        const float b0 = Exp2(fmaf(__uint_as_float(rb[i]), p.scale_log2, neg_m));
+                        const float b1 = Exp2(fmaf(__uint_as_float(rb[i + 1]), p.scale_log2, neg_m));
+                        part4[0] += a0;
+                        part4[1] += a1;
+                        part4[2] += b0;
+                        part4[3] += b1;
+                        pk[i / 2] = Pack2<T>(a0, a1);
+                        pk[16 + i / 2] = Pack2<T>(b0, b1);
+                    }
+                    TmemSt32(s_addr + half * 32, pk);
+                }
+                l_sum += (part4[0] + part4[1]) + (part4[2] + part4[3]);
+                TmemWaitSt();
+                TcFenceBefore();
+                MbarArrive(bar(kPFull + t));
+            }
+            if (!ok) break;
+
+            // ---- epilogue: O / l -> global, optional LSE; O is handed back as soon as it is in registers ----
+            ok = __all_sync(0xffffffffu, MbarWait(bar(kODone + t), (steps - 1) & 1u, abort_flag));
+            if (!ok) break;
+            TcFenceAfter();
+            const float inv = l_sum > 0.0f ? 1.0f / l_sum : 0.0f;
+            T* o_row = reinterpret_cast<T*>(p.out) + w.b * p.o_sb + w.h * p.o_sh + static_cast<int64_t>(row) * p.o_ss;
+#pragma unroll
+            for (int cblk = 0; cblk < DP / 32; ++cblk) {
+                uint32_t r[32];
+                TmemLd32(o_addr + cblk * 32, r);
+                TmemWaitLd();
+                if (cblk == DP / 32 - 1) {
+                    TcFenceBefore();
+                    MbarArrive(bar(kOFree + t));
+                }
+                if (row < p.seq_q) {
+#pragma unroll
+                    for (int v8 = 0; v8 < 4; ++v8) {
+                        const int d0 = cblk * 32 + v8 * 8;
+                        if (d0 < p.head_dim) {
+                            uint4 pk;
+                            pk.x = Pack2<T>(__uint_as_float(r[v8 * 8 + 0]) * inv, __uint_as_float(r[v8 * 8 + 1]) * inv);
+                            pk.y = Pack2<T>(__uint_as_float(r[v8 * 8 + 2]) * inv, __uint_as_float(r[v8 * 8 + 3]) * inv);
+                            pk.z = Pack2<T>(__uint_as_float(r[v8 * 8 + 4]) * inv, __uint_as_float(r[v8 * 8 + 5]) * inv);
+                            pk.w = Pack2<T>(__uint_as_float(r[v8 * 8 + 6]) * inv, __uint_as_float(r[v8 * 8 + 7]) * inv);
+                            *reinterpret_cast<uint4*>(o_row + d0) = pk;
+                        }
+                    }
+                }
+            }
+            if (p.lse != nullptr && row < p.seq_q) {
+                p.lse[(static_cast<int64_t>(w.b) * p.heads + w.h) * p.seq_q + row] =
+                    l_sum > 0.0f ? (m_ref + log2f(l_sum)) * kLn2 : -CUDART_INF_F;
             }
         }
         failed = !ok;
@@ -522,7 +572,8 @@ int LaunchFlash(const ScaFlashFwdParams& f, float* debug_s, cudaStream_t stream)
     }
     const void* fn = reinterpret_cast<const void*>(&flash_fwd_sm100_kernel<T, DP, QT, BN>);
     if (int rc = EnsureDynamicSmem(fn, G::kSmemBytes, "flash_fwd_sm100_kernel")) return rc;
-    flash_fwd_sm100_kernel<T, DP, QT, BN><<<static_cast<unsigned>(ctas), kFlashThreads, G::kSmemBytes, stream>>>(map_q, map_k, map_v, p);
+    const unsigned grid = static_cast<unsigned>(std::min<int64_t>(ctas, SmCount()));  // one persistent CTA per SM
+    flash_fwd_sm100_kernel<T, DP, QT, BN><<<grid, kFlashThreads, G::kSmemBytes, stream>>>(map_q, map_k, map_v, p);
     return CheckLaunch("flash_fwd_sm100_kernel", stream);
 }
 
