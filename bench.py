@@ -114,12 +114,18 @@ class Workload:
     def e2e_step(self): ...               # H2D + step + D2H; returns nothing
     def cpu_sample(self, threads, impl): ...  # -> (work_done, seconds, description, kind)
 
+    def traffic(self):
+        return getattr(self, "traffic_bytes", None)
+
 
 class DecodeWorkload(Workload):
     name = "splitk_decode_B128_Skv4096_Hq32_Hkv8_D128_bf16"
     metric, unit, bound = "decode_kv_bandwidth", "GB/s", "hbm"
     launches_per_step = 2  # partial + merge
     B, SKV = 128, 4096
+    # dram__bytes_read + dram__bytes_write of decode_partial_kernel, ncu capture at B=16 scaled x8
+    # (profiles/decode_splitk_c3.md); traffic grows in proportion to the batch
+    traffic_bytes = (268.61e6 + 5.8e6) * 8
 
     def setup(self, torch, device, seed):
         from scicompute_attention_b200 import ops
@@ -158,7 +164,9 @@ class DecodeWorkload(Workload):
 
     def cpu_sample(self, threads, impl):
         import numpy as np
-        nb = max(1, min(self.B, threads))  # one sequence per host thread
+        # CPU leg of the main arm: the whole batch (a second or two of FP64 work on all host threads);
+        # one step of the reference arm: eight sequences per host thread of the reference's own routine
+        nb = self.q.shape[0] if impl == "port" else max(1, min(self.q.shape[0], 8 * threads))
         q = self.q[:nb].float().cpu().numpy()
         k = self.k[:nb].float().cpu().numpy()
         v = self.v[:nb].float().cpu().numpy()
@@ -172,6 +180,9 @@ class PagedWorkload(Workload):
     metric, unit, bound = "paged_decode_kv_bandwidth", "GB/s", "hbm"
     launches_per_step = 3  # batched append + partial + merge
     NSEQ, BS, NBLK = 256, 16, 160000
+    # ncu capture of the paged decode_partial_kernel on 32 sequences: 606.3 MB moved for 597.7 MB of K/V
+    # (profiles/paged_decode_c4.md); scaled by the tokens of the full batch in roofline()
+    traffic_ratio = (598.10e6 + 8.21e6) / 597.75e6
 
     def setup(self, torch, device, seed):
         import numpy as np
@@ -214,6 +225,9 @@ class PagedWorkload(Workload):
         pages = int(sum(-(-(int(n) + 1) // self.BS) for n in self.lens))
         return toks * (2 * HKV * D * 2) + 2 * self.NSEQ * HQ * D * 2 + pages * 4 + self.NSEQ * 4
 
+    def traffic(self):
+        return float((self.lens + 1).sum()) * 2 * HKV * D * 2 * self.traffic_ratio
+
     def config(self):
         return {"workload": self.name, "num_seqs": self.NSEQ, "block_size": self.BS, "pool_blocks": self.NBLK,
                 "tokens_attended": int((self.lens + 1).sum()), "heads_q": HQ, "heads_kv": HKV, "head_dim": D,
@@ -239,8 +253,9 @@ class PagedWorkload(Workload):
 
     def cpu_sample(self, threads, impl):
         np, torch = self.np, self.torch
-        # bounded sample: the `threads` shortest... no: the first sequences, gathered into contiguous K/V
-        ns = max(1, min(8, threads))
+        # bounded sample: the first sequences, gathered into contiguous K/V (64 for the main arm's CPU leg,
+        # two per host thread for one step of the reference arm)
+        ns = max(1, min(self.q.shape[0], 64 if impl == "port" else 2 * threads))
         work = 0
         qs, ks, vs = [], [], []
         for s in range(ns):
@@ -265,6 +280,9 @@ class FlashWorkload(Workload):
     metric, unit, bound = "flash_prefill_throughput", "TFLOP/s", "tensor"
     launches_per_step = 1
     B, S = 4, 4096
+    # dram__bytes_read + dram__bytes_write of flash_fwd_sm100_kernel, ncu capture at B=1 scaled x4
+    # (profiles/flash_prefill_c2.md); the output mostly stays in L2 until after the kernel
+    traffic_bytes = (50.40e6 + 2.8e6) * 4
 
     def setup(self, torch, device, seed):
         from scicompute_attention_b200 import ops
@@ -305,10 +323,12 @@ class FlashWorkload(Workload):
         self.ho.copy_(self.out, non_blocking=True)
 
     def cpu_sample(self, threads, impl):
-        # bounded sample: one (batch, head) pair per host thread, the last 64 query rows of a
-        # 1024-token causal prefix (rows i attend to i + 1 keys); FLOPs counted for those rows only
+        # bounded sample: one (batch 0, head) pair per host thread; the main arm's CPU leg takes whole
+        # causal heads (all 4096 rows), one step of the reference arm the last 256 query rows (rows i attend to
+        # i + 1 keys); FLOPs are counted for the sampled rows only
         import numpy as np
-        sq, skv = 64, 1024
+        skv = self.q.shape[2]
+        sq = skv if impl == "port" else min(256, skv)
         nh = max(1, min(HQ, threads))
         q = self.q[:1, :nh, skv - sq:skv].float().cpu().numpy()
         k = self.k[:1, :HKV, :skv].float().cpu().numpy()
@@ -469,7 +489,8 @@ def main():
             "config": wl.config(),
             "roofline": {"bound": wl.bound, "achieved": per_gpu, "peak": peak, "unit": wl.unit,
                          "frac": per_gpu / peak, "peak_source": peaks["source"],
-                         "frac_of_nominal": per_gpu / nominal, "traffic": None},
+                         "frac_of_nominal": per_gpu / nominal, "traffic": wl.traffic(),
+                         "traffic_unit": "bytes per launch of the dominant kernel (ncu capture, scaled; see profiles/)"},
             "cpu_baseline": cpu,
             "e2e": {"value": e2e_value, "unit": wl.unit, "h2d_bytes_per_step": wl.h2d, "d2h_bytes_per_step": wl.d2h,
                     "ms_per_step": e2e_ms, "steps": e2e_steps},
@@ -497,11 +518,11 @@ def reference_arm(args, rank, world, threads):
     # host tensors with the workload's shapes, reduced to the sample the CPU leg consumes
     g = torch.Generator().manual_seed(args.seed)
     if isinstance(wl, FlashWorkload):
-        wl.q = torch.randn((1, HQ, 1024, D), generator=g).to(torch.bfloat16)
-        wl.k = torch.randn((1, HKV, 1024, D), generator=g).to(torch.bfloat16)
-        wl.v = torch.randn((1, HKV, 1024, D), generator=g).to(torch.bfloat16)
+        wl.q = torch.randn((1, HQ, wl.S, D), generator=g).to(torch.bfloat16)
+        wl.k = torch.randn((1, HKV, wl.S, D), generator=g).to(torch.bfloat16)
+        wl.v = torch.randn((1, HKV, wl.S, D), generator=g).to(torch.bfloat16)
     elif isinstance(wl, DecodeWorkload):
-        nb = max(1, min(wl.B, threads))
+        nb = max(1, min(wl.B, 8 * threads))
         wl.q = torch.randn((nb, HQ, 1, D), generator=g).to(torch.bfloat16)
         wl.k = torch.randn((nb, HKV, wl.SKV, D), generator=g).to(torch.bfloat16)
         wl.v = torch.randn((nb, HKV, wl.SKV, D), generator=g).to(torch.bfloat16)
@@ -509,7 +530,7 @@ def reference_arm(args, rank, world, threads):
         rng = np.random.default_rng(args.seed)
         wl.np, wl.torch = np, torch
         wl.lens = rng.integers(512, 8193, size=wl.NSEQ).astype(np.int64)
-        ns = max(1, min(8, threads))
+        ns = max(1, min(wl.NSEQ, 2 * threads))
         need = int(sum(-(-(int(n) + 1) // wl.BS) for n in wl.lens[:ns]))
         wl.k_pool = torch.randn((need, wl.BS, HKV, D), generator=g).to(torch.bfloat16)
         wl.v_pool = torch.randn((need, wl.BS, HKV, D), generator=g).to(torch.bfloat16)
