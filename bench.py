@@ -15,6 +15,8 @@ Workloads (shapes of a Qwen3-4B attention layer: H_q = 32, H_kv = 8, D = 128):
   decode  split-K decode, B = 128, S_kv = 4096, bf16  -> GB/s over bytes(K) + bytes(V) + bytes(Q) + bytes(O)
   paged   256 sequences, lengths U[512, 8192], 16-token pages in a 160k-block pool with a shuffled
           free list; one token appended per sequence, then attended -> GB/s over the KV bytes read
+  longctx B = 8, S_kv = 131072 with the KV sequence split over the ranks (strong scaling), partial
+          (m, l, O) triples merged after one NCCL all-gather -> GB/s over the whole K/V
 """
 from __future__ import annotations
 
@@ -340,7 +342,65 @@ class FlashWorkload(Workload):
         return flops, secs, f"{nh} heads x last {sq} query rows of a {skv}-token causal prefix", kind
 
 
-WORKLOADS = {"flash": FlashWorkload, "decode": DecodeWorkload, "paged": PagedWorkload}
+class LongContextWorkload(Workload):
+    """Sequence-split decode: B = 8, S_kv = 131072; the KV axis is cut into one contiguous slice per rank,
+    every rank reduces its slice to (m, l, O) triples, one all-gather of B*H_q*(2+D) floats per rank moves
+    them, and every rank merges. Total work is fixed, so this workload scales "strong"."""
+    name = "seqsplit_decode_B8_Skv131072_Hq32_Hkv8_D128_bf16"
+    metric, unit, bound = "longctx_decode_kv_bandwidth", "GB/s", "hbm"
+    launches_per_step = 4  # partial + merge-to-triples (+ all-gather) + merge across ranks
+    scaling = "strong"
+    B, SKV = 8, 131072
+    traffic_bytes = None
+
+    def setup(self, torch, device, seed):
+        import torch.distributed as dist
+        from scicompute_attention_b200 import multi_gpu, ops
+        self.torch, self.ops, self.mg = torch, ops, multi_gpu
+        self.rank = dist.get_rank() if dist.is_initialized() else 0
+        self.world = dist.get_world_size() if dist.is_initialized() else 1
+        lo, hi = multi_gpu.kv_range_for_rank(self.SKV, self.rank, self.world)
+        g = torch.Generator(device=device).manual_seed(1234)  # q is replicated: same seed on every rank
+        self.q = torch.randn((self.B, HQ, 1, D), generator=g, device=device, dtype=torch.float32).to(torch.bfloat16)
+        g2 = torch.Generator(device=device).manual_seed(seed + 77)
+        self.k = torch.randn((self.B, HKV, hi - lo, D), generator=g2, device=device, dtype=torch.bfloat16)
+        self.v = torch.randn((self.B, HKV, hi - lo, D), generator=g2, device=device, dtype=torch.bfloat16)
+
+    def step(self):
+        self.out = self.mg.sequence_split_decode(self.q, self.k, self.v)
+
+    def work_per_step(self):
+        # whole job: all ranks together read the full K and V once
+        return 2 * self.B * HKV * self.SKV * D * 2 + 2 * self.B * HQ * D * 2
+
+    def config(self):
+        return {"workload": self.name, "batch": self.B, "seq_kv": self.SKV, "heads_q": HQ, "heads_kv": HKV,
+                "head_dim": D, "l2_policy": "inputs larger than L2 (4.3 GB over all ranks)",
+                "sharding": "KV sequence split across ranks; one all-gather of (m, l, O) triples per step"}
+
+    def e2e_setup(self, torch):
+        self.hq = self.q.cpu().pin_memory()
+        self.ho = torch.empty((self.B * HQ, D), dtype=torch.bfloat16).pin_memory()
+        self.h2d, self.d2h = self.hq.numel() * 2, self.ho.numel() * 2
+
+    def e2e_step(self):
+        # a decode step moves the new query up and the attention output down; the KV cache lives on the devices
+        self.q.copy_(self.hq, non_blocking=True)
+        self.step()
+        self.ho.copy_(self.out, non_blocking=True)
+
+    def cpu_sample(self, threads, impl):
+        nb = 1
+        skv = 16384
+        q = self.q[:nb].float().cpu().numpy()
+        k = self.k[:nb, :, :skv].float().cpu().numpy()
+        v = self.v[:nb, :, :skv].float().cpu().numpy()
+        secs, kind = run_cpu_attention(q, k, v, True, threads, impl)
+        work = 2 * nb * HKV * k.shape[2] * D * 2 + 2 * nb * HQ * D * 2
+        return work, secs, f"{nb} of {self.B} sequences, first {k.shape[2]} of {self.SKV} keys, all heads", kind
+
+
+WORKLOADS = {"flash": FlashWorkload, "decode": DecodeWorkload, "paged": PagedWorkload, "longctx": LongContextWorkload}
 DEFAULT_WORKLOAD = "flash"
 
 
@@ -469,9 +529,10 @@ def main():
     ms_step = ms_total / args.steps
     work = wl.work_per_step()
     scale = 1e9 if wl.unit == "GB/s" else 1e12
-    per_gpu = work / (ms_step * 1e-3) / scale
-    value = per_gpu * world
-    e2e_value = work / (e2e_ms * 1e-3) / scale * world if e2e_ms else None
+    strong = getattr(wl, "scaling", "weak") == "strong"   # strong: `work` is already the whole job
+    value = work / (ms_step * 1e-3) / scale * (1 if strong else world)
+    per_gpu = value / world
+    e2e_value = (work / (e2e_ms * 1e-3) / scale * (1 if strong else world)) if e2e_ms else None
 
     if rank == 0:
         peaks = measured_peaks()
@@ -484,7 +545,7 @@ def main():
                    "sample": desc + f" ({cs:.1f} s of FP64 host work)"}
         line = {
             "metric": wl.metric, "value": value, "unit": wl.unit, "n_gpus": world, "steps": args.steps,
-            "warmup": args.warmup, "ms_per_step": ms_step, "higher_is_better": True, "scaling": "weak",
+            "warmup": args.warmup, "ms_per_step": ms_step, "higher_is_better": True, "scaling": getattr(wl, "scaling", "weak"),
             "vs_baseline": None, "dtype": "bf16", "data": "synthetic (seeded iid N(0,1), random page tables)",
             "config": wl.config(),
             "roofline": {"bound": wl.bound, "achieved": per_gpu, "peak": peak, "unit": wl.unit,
@@ -521,6 +582,10 @@ def reference_arm(args, rank, world, threads):
         wl.q = torch.randn((1, HQ, wl.S, D), generator=g).to(torch.bfloat16)
         wl.k = torch.randn((1, HKV, wl.S, D), generator=g).to(torch.bfloat16)
         wl.v = torch.randn((1, HKV, wl.S, D), generator=g).to(torch.bfloat16)
+    elif isinstance(wl, LongContextWorkload):
+        wl.q = torch.randn((1, HQ, 1, D), generator=g).to(torch.bfloat16)
+        wl.k = torch.randn((1, HKV, 16384, D), generator=g).to(torch.bfloat16)
+        wl.v = torch.randn((1, HKV, 16384, D), generator=g).to(torch.bfloat16)
     elif isinstance(wl, DecodeWorkload):
         nb = max(1, min(wl.B, 8 * threads))
         wl.q = torch.randn((nb, HQ, 1, D), generator=g).to(torch.bfloat16)

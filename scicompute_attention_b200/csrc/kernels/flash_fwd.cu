@@ -9,7 +9,7 @@
 //     tensor core works on one tile while the other tile's softmax runs;
 //   * warp 0 is the TMA producer: Q tiles once, then K_j, V_j, K_j+1, ... into a ring of 128-byte
 //     swizzled shared-memory slots, each guarded by a full/empty mbarrier pair. Loads are plain
-//     per-CTA tensor loads (no cluster multicast); K/V reuse between the CTAs of a kv head comes
+//     per-CTA tensor loads (one CTA, one destination); K/V reuse between the CTAs of a kv head comes
 //     from L2. Rows past the end of a sequence are zero-filled by the TMA unit;
 //   * warp 1 issues every tcgen05.mma from one thread: S_t = Q_t K_j^T (both operands in shared
 //     memory, K-major) into tensor memory, and O_t += P_t V_j with P_t read from tensor memory and

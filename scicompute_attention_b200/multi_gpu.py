@@ -8,7 +8,7 @@ Two schemes, as the workload dictates:
     unnormalised (m, l, O[D]) triple per (batch, head), one small all-gather moves the triples
     (B * H_q * (2 + D) floats per rank), and every rank merges them with the same max-rescaled rule the
     split-K merge kernel uses.
-No kernel here reads a peer's memory and no TMA multicast is involved; the only cross-GPU traffic is the
+No kernel here reads a peer's memory; every TMA load is a plain per-CTA load; the only cross-GPU traffic is the
 all-gather.
 """
 from __future__ import annotations

@@ -1,0 +1,60 @@
+"""Sequence-split decode on two real GPUs: each rank runs the CUDA triples operator on its KV slice, NCCL
+all-gathers the triples, each rank merges on the device; the result must match the FP64 oracle on the unsplit
+sequence. In-switch reduction is switched off (NCCL_NVLS_ENABLE=0): the path only needs a plain all-gather.
+Skipped when fewer than two GPUs are visible."""
+import os
+import socket
+import sys
+
+import numpy as np
+import pytest
+
+pytestmark = pytest.mark.gpu
+
+
+def _worker(rank, world, port, result_dir):
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    os.environ["NCCL_NVLS_ENABLE"] = "0"
+    here = os.path.dirname(os.path.abspath(__file__))
+    for p in (os.path.dirname(here), here, os.path.join(os.path.dirname(here), "oracle")):
+        if p not in sys.path:
+            sys.path.insert(0, p)
+    import torch
+    import torch.distributed as dist
+
+    import helpers as H
+    import oracle_lib as ol
+    from scicompute_attention_b200 import multi_gpu as mg
+
+    torch.cuda.set_device(rank)
+    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=torch.device("cuda", rank))
+    dt, b, hq, hkv, skv, d = ol.DT_BF16, 2, 32, 8, 3001, 128
+    qb, qd = H.normal_inputs((b, hq, 1, d), 11, dt)
+    kb, kd = H.normal_inputs((b, hkv, skv, d), 12, dt)
+    vb, vd = H.normal_inputs((b, hkv, skv, d), 13, dt)
+    lo, hi = mg.kv_range_for_rank(skv, rank, world)
+    q = H.to_device(qb, dt, f"cuda:{rank}")
+    k = H.to_device(np.ascontiguousarray(kb[:, :, lo:hi]), dt, f"cuda:{rank}")
+    v = H.to_device(np.ascontiguousarray(vb[:, :, lo:hi]), dt, f"cuda:{rank}")
+    out = mg.sequence_split_decode(q, k, v)
+    torch.cuda.synchronize()
+    expect = ol.attention_f64(qd, kd, vd, causal=True)
+    H.check_close(H.to_host_f32(out).reshape(b, hq, 1, d), expect, dt, f"sequence-split decode rank {rank}")
+    with open(os.path.join(result_dir, f"ok{rank}"), "w") as f:
+        f.write("ok")
+    dist.barrier()
+    dist.destroy_process_group()
+
+
+def test_sequence_split_decode_over_nccl(tmp_path):
+    import torch
+    import torch.multiprocessing as mp
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs two GPUs")
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", 0))
+        port = s.getsockname()[1]
+    world = 2
+    mp.spawn(_worker, args=(world, port, str(tmp_path)), nprocs=world, join=True)
+    assert all(os.path.exists(tmp_path / f"ok{r}") for r in range(world))
