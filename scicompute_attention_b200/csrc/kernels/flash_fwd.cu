@@ -5,8 +5,9 @@
 // tile). Same arithmetic contract - fp16/bf16 inputs, fp32 accumulation, online softmax through
 // exp2, bottom-right aligned causal mask, GQA, optional log-sum-exp - on a Blackwell execution plan:
 //
-//   * one CTA owns 256 query rows of one (batch, head): two 128-row tiles that ping-pong, so the
-//     tensor core works on one tile while the other tile's softmax runs;
+//   * one persistent CTA per SM walks a list of work items; an item is 256 query rows of one
+//     (batch, head): two 128-row tiles that ping-pong, so the tensor core works on one tile while
+//     the other tile's softmax runs;
 //   * warp 0 is the TMA producer: Q tiles once, then K_j, V_j, K_j+1, ... into a ring of 128-byte
 //     swizzled shared-memory slots, each guarded by a full/empty mbarrier pair. Loads are plain
 //     per-CTA tensor loads (one CTA, one destination); K/V reuse between the CTAs of a kv head comes
@@ -15,9 +16,11 @@
 //     memory, K-major) into tensor memory, and O_t += P_t V_j with P_t read from tensor memory and
 //     V_j as an MN-major shared-memory operand (no transposition of V anywhere);
 //   * warps 4-7 and 8-11 are the two softmax groups, one thread per query row: they read their S row
-//     from tensor memory, keep the running max / sum in registers, write P back over S as packed
-//     16-bit values, and rescale O in tensor memory only when the running max moved by more than
-//     2^8 (the final division by the row sum absorbs the stale reference point exactly);
+//     from tensor memory once, 64 columns at a time, exponentiate against the reference point the
+//     row already has, keep the running sum in registers and write P back over S as packed 16-bit
+//     values. The reference point moves (and O, the sum and the part of P already written are
+//     rescaled) only when a half-row exceeds it by more than 2^8; the final division by the row sum
+//     absorbs the stale reference point exactly;
 //   * tensor memory: S_0 | S_1 | O_0 | O_1, 128 (or D) fp32 columns each, 512 columns in total.
 //
 // Every wait on an mbarrier is bounded (sm100.cuh): on expiry the role raises a CTA-wide abort flag,
@@ -39,6 +42,17 @@ namespace {
 using namespace sm100;
 
 constexpr int kBlockM = 128;
+
+template <typename T>
+__device__ __forceinline__ float2 Unpack2(uint32_t v);
+template <>
+__device__ __forceinline__ float2 Unpack2<__nv_bfloat16>(uint32_t v) {
+    return make_float2(__uint_as_float(v << 16), __uint_as_float(v & 0xffff0000u));
+}
+template <>
+__device__ __forceinline__ float2 Unpack2<__half>(uint32_t v) {
+    return __half22float2(*reinterpret_cast<const __half2*>(&v));
+}
 constexpr int kFlashThreads = 384;   // warp 0 TMA, 1 MMA, 2 TMEM owner, 3 idle, 4-7 / 8-11 softmax
 constexpr int kTmemColumns = 512;
 constexpr float kRescaleThreshold = 8.0f;  // log2 domain: P stays <= 2^8
@@ -115,8 +129,10 @@ flash_fwd_sm100_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
     const int warp = threadIdx.x >> 5;
     const int lane = threadIdx.x & 31;
 
-    // ---- work items: (query block, batch*head), heaviest causal blocks first; a CTA walks the list with
-    // stride gridDim.x so that the loads of its next item overlap the tail of the current one ----------
+    // ---- work items: (query block, batch*head), heaviest causal blocks first. The list is dealt to the
+    // CTAs in rounds of gridDim.x items, every other round in reverse CTA order, so that the CTA that got
+    // the heaviest item of one round gets the lightest of the next (the static schedule then ends within
+    // about one KV tile of each other on all SMs). Every role of a CTA walks the same sequence. ----------
     const int bh_count = p.batch * p.heads;
     const int total_items = p.m_blocks * bh_count;
     struct Item {
@@ -138,6 +154,12 @@ flash_fwd_sm100_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
         w.ntiles[1] = QT > 1 ? TilesFor<BN>(p, w.m0[1]) : 0;
         w.n_max = max(w.ntiles[0], w.ntiles[1]);
         return w;
+    };
+    const int rounds = (total_items + gridDim.x - 1) / gridDim.x;
+    auto item_of_round = [&](int r) {  // -1: this CTA has no item in round r (only in the last, partial round)
+        const int pos = (r & 1) ? static_cast<int>(gridDim.x - 1 - blockIdx.x) : static_cast<int>(blockIdx.x);
+        const int idx = r * static_cast<int>(gridDim.x) + pos;
+        return idx < total_items ? idx : -1;
     };
 
     if (threadIdx.x == 0) {
@@ -176,7 +198,9 @@ flash_fwd_sm100_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
             uint32_t q_uses[2] = {0, 0};   // how often each query buffer has been filled so far
             uint32_t kv_loads = 0;         // K/V tiles loaded so far (ring position)
             bool ok = true;
-            for (int idx = blockIdx.x; idx < total_items && ok; idx += gridDim.x) {
+            for (int r = 0; r < rounds && ok; ++r) {
+                const int idx = item_of_round(r);
+                if (idx < 0) continue;
                 const Item w = decode_item(idx);
                 for (int t = 0; t < QT && ok; ++t) {
                     if (w.ntiles[t] == 0) continue;
@@ -243,7 +267,9 @@ flash_fwd_sm100_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
             uint32_t steps[2] = {0, 0};     // KV tiles processed per query tile (phase of s_full / p_full / o_done)
             uint32_t kv_base = 0;           // ring position of this item's K_0
             bool ok = true;
-            for (int idx = blockIdx.x; idx < total_items && ok; idx += gridDim.x) {
+            for (int r = 0; r < rounds && ok; ++r) {
+                const int idx = item_of_round(r);
+                if (idx < 0) continue;
                 const Item w = decode_item(idx);
                 auto slot_of = [&](int it) { return (kv_base + it) % G::kSlots; };
                 auto phase_of = [&](int it) { return ((kv_base + it) / G::kSlots) & 1u; };
@@ -307,7 +333,9 @@ flash_fwd_sm100_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
         uint32_t steps = 0;  // KV tiles this group has processed (phase of s_full / p_full / o_done)
         bool ok = true;
 
-        for (int idx = blockIdx.x; idx < total_items && ok && t < QT; idx += gridDim.x) {
+        for (int r = 0; r < rounds && ok && t < QT; ++r) {
+            const int idx = item_of_round(r);
+            if (idx < 0) continue;
             const Item w = decode_item(idx);
             const int n_t = w.ntiles[t];
             if (n_t == 0) continue;
@@ -319,17 +347,18 @@ flash_fwd_sm100_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
                 ok = __all_sync(0xffffffffu, MbarWait(bar(kSFull + t), steps & 1u, abort_flag));
                 if (!ok) break;
                 TcFenceAfter();
-                // Two passes over the S row, 64 columns at a time, so that a thread never holds more than 64
-                // scores: pass 1 finds the row max, pass 2 re-reads S, exponentiates and writes P. P (16-bit
-                // pairs) lands on the first BN / 2 columns of S_t; the half-row written in step h only covers
-                // columns that step h has already consumed.
+                // One pass over the S row, 64 columns at a time. The exponentials use the reference point the row
+                // already has; the half's own max is only checked against it. If a half exceeds the reference by
+                // more than the threshold (always true for the first half of an item), the reference moves and
+                // whatever was accumulated under the old one is rescaled: O, the row sum and the half of P that
+                // this step has already written. P (16-bit pairs) lands on the first BN / 2 columns of S_t;
+                // the half-row written in step h only covers columns that step h has already consumed.
                 const int col0 = j * BN;
                 const int kv_limit = p.seq_kv - col0;                                   // columns >= kv_limit do not exist
                 const int causal_limit = p.causal ? (row + p.diagonal - col0 + 1) : BN;  // columns >= limit are masked
                 const int limit = min(kv_limit, causal_limit);
                 const bool ragged = limit < BN;
-
-                float mx4[4] = {-CUDART_INF_F, -CUDART_INF_F, -CUDART_INF_F, -CUDART_INF_F};
+                float part4[4] = {0.0f, 0.0f, 0.0f, 0.0f};  // this step's share of the row sum
     #pragma unroll
                 for (int half = 0; half < BN / 64; ++half) {
                     uint32_t ra[32], rb[32];
@@ -351,6 +380,7 @@ flash_fwd_sm100_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
                             if (half * 64 + 32 + i >= limit) rb[i] = 0xff800000u;
                         }
                     }
+                    float mx4[4] = {-CUDART_INF_F, -CUDART_INF_F, -CUDART_INF_F, -CUDART_INF_F};
     #pragma unroll
                     for (int i = 0; i < 32; i += 4) {
     #pragma unroll
@@ -358,43 +388,42 @@ flash_fwd_sm100_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
                             mx4[e] = fmaxf(mx4[e], fmaxf(__uint_as_float(ra[i + e]), __uint_as_float(rb[i + e])));
                         }
                     }
-                }
-                const float mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3])) * p.scale_log2;  // scale > 0
-                const float m_new = fmaxf(m_ref, mx);
-                // Move the reference point only when it is far off; O and l are rescaled to match.
-                const bool move = (j == 0) || (m_new - m_ref > kRescaleThreshold);
-                if (j > 0 && __any_sync(0xffffffffu, move)) {
-                    ok = __all_sync(0xffffffffu, MbarWait(bar(kODone + t), (steps - 1) & 1u, abort_flag));
-                    if (!ok) break;
-                    TcFenceAfter();
-                    const float alpha = move ? Exp2(m_ref - m_new) : 1.0f;  // m_ref = -inf -> 0
+                    const float mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3])) * p.scale_log2;  // scale > 0
+                    const bool move = mx > m_ref + kRescaleThreshold;  // false for a fully masked half (-inf)
+                    if (__any_sync(0xffffffffu, move)) {
+                        const float alpha = move ? Exp2(m_ref - mx) : 1.0f;  // m_ref = -inf -> 0
+                        if (j > 0) {
+                            ok = __all_sync(0xffffffffu, MbarWait(bar(kODone + t), (steps - 1) & 1u, abort_flag));
+                            if (!ok) break;
+                            TcFenceAfter();
+    #pragma unroll 1
+                            for (int cblk = 0; cblk < DP / 32; ++cblk) {
+                                uint32_t r[32];
+                                TmemLd32(o_addr + cblk * 32, r);
+                                TmemWaitLd();
     #pragma unroll
-                    for (int cblk = 0; cblk < DP / 32; ++cblk) {
-                        uint32_t r[32];
-                        TmemLd32(o_addr + cblk * 32, r);
-                        TmemWaitLd();
-    #pragma unroll
-                        for (int i = 0; i < 32; ++i) r[i] = __float_as_uint(__uint_as_float(r[i]) * alpha);
-                        TmemSt32(o_addr + cblk * 32, r);
-                    }
-                    l_sum *= alpha;
-                }
-                if (move) m_ref = m_new;
-                const float neg_m = (m_ref == -CUDART_INF_F) ? 0.0f : -m_ref;
-                float part4[4] = {0.0f, 0.0f, 0.0f, 0.0f};
-    #pragma unroll
-                for (int half = 0; half < BN / 64; ++half) {
-                    uint32_t ra[32], rb[32];
-                    TmemLd32(s_addr + half * 64, ra);
-                    TmemLd32(s_addr + half * 64 + 32, rb);
-                    TmemWaitLd();
-                    if (ragged) {
-    #pragma unroll
-                        for (int i = 0; i < 32; ++i) {
-                            if (half * 64 + i >= limit) ra[i] = 0xff800000u;
-                            if (half * 64 + 32 + i >= limit) rb[i] = 0xff800000u;
+                                for (int i = 0; i < 32; ++i) r[i] = __float_as_uint(__uint_as_float(r[i]) * alpha);
+                                TmemSt32(o_addr + cblk * 32, r);
+                            }
                         }
+                        l_sum *= alpha;
+    #pragma unroll
+                        for (int e = 0; e < 4; ++e) part4[e] *= alpha;
+                        if (half > 0) {  // the first half of P was written under the old reference
+                            uint32_t q[32];
+                            TmemWaitSt();
+                            TmemLd32(s_addr, q);
+                            TmemWaitLd();
+    #pragma unroll
+                            for (int i = 0; i < 32; ++i) {
+                                const float2 f = Unpack2<T>(q[i]);
+                                q[i] = Pack2<T>(f.x * alpha, f.y * alpha);
+                            }
+                            TmemSt32(s_addr, q);
+                        }
+                        if (move) m_ref = mx;
                     }
+                    const float neg_m = (m_ref == -CUDART_INF_F) ? 0.0f : -m_ref;
                     uint32_t pk[32];
     #pragma unroll
                     for (int i = 0; i < 32; i += 2) {
@@ -411,6 +440,7 @@ flash_fwd_sm100_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
                     }
                     TmemSt32(s_addr + half * 32, pk);
                 }
+                if (!ok) break;
                 l_sum += (part4[0] + part4[1]) + (part4[2] + part4[3]);
                 TmemWaitSt();
                 TcFenceBefore();

@@ -39,16 +39,19 @@ __device__ __forceinline__ void MbarArrive(uint32_t bar) {
 __device__ __forceinline__ void MbarExpectTx(uint32_t bar, uint32_t bytes) {
     asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
 }
+// One probe of the barrier. The hint lets the hardware park the thread for up to that many nanoseconds
+// instead of returning at once, so that a waiting warp does not take issue slots from the warps that work.
+constexpr uint32_t kTryWaitHintNs = 20000;
 __device__ __forceinline__ bool MbarTryWait(uint32_t bar, uint32_t parity) {
     uint32_t done;
     asm volatile(
         "{\n"
         ".reg .pred p;\n"
-        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n"
         "selp.u32 %0, 1, 0, p;\n"
         "}\n"
         : "=r"(done)
-        : "r"(bar), "r"(parity)
+        : "r"(bar), "r"(parity), "r"(kTryWaitHintNs)
         : "memory");
     return done != 0;
 }
@@ -132,7 +135,6 @@ __device__ __forceinline__ void TmemSt32(uint32_t taddr, const uint32_t (&r)[32]
           "r"(r[24]), "r"(r[25]), "r"(r[26]), "r"(r[27]), "r"(r[28]), "r"(r[29]), "r"(r[30]), "r"(r[31])
         : "memory");
 }
-
 // ---- tcgen05.mma (dense f16/bf16 inputs, f32 accumulate, one CTA) -----------------------------------
 enum : uint32_t { kFmtF16 = 0, kFmtBf16 = 1 };
 
