@@ -15,8 +15,9 @@ Workloads (shapes of a Qwen3-4B attention layer: H_q = 32, H_kv = 8, D = 128):
   decode  split-K decode, B = 128, S_kv = 4096, bf16  -> GB/s over bytes(K) + bytes(V) + bytes(Q) + bytes(O)
   paged   256 sequences, lengths U[512, 8192], 16-token pages in a 160k-block pool with a shuffled
           free list; one token appended per sequence, then attended -> GB/s over the KV bytes read
-  longctx B = 8, S_kv = 131072 with the KV sequence split over the ranks (strong scaling), partial
-          (m, l, O) triples merged after one NCCL all-gather -> GB/s over the whole K/V
+  longctx B = 8, S_kv = 131072 with the KV sequence split over the ranks (strong scaling); the partial
+          (m, l, O) triples cross NVLink inside one merge kernel over peer-mapped buffers
+          (--exchange nccl: one NCCL all-gather between two kernels) -> GB/s over the whole K/V
 """
 from __future__ import annotations
 
@@ -344,14 +345,16 @@ class FlashWorkload(Workload):
 
 class LongContextWorkload(Workload):
     """Sequence-split decode: B = 8, S_kv = 131072; the KV axis is cut into one contiguous slice per rank,
-    every rank reduces its slice to (m, l, O) triples, one all-gather of B*H_q*(2+D) floats per rank moves
-    them, and every rank merges. Total work is fixed, so this workload scales "strong"."""
+    every rank reduces its slice to (m, l, O) triples, B*H_q*(2+D) floats per rank travel to every peer
+    (stored by the merge kernel into peer-mapped buffers, or by one NCCL all-gather), and every rank merges.
+    Total work is fixed, so this workload scales "strong"."""
     name = "seqsplit_decode_B8_Skv131072_Hq32_Hkv8_D128_bf16"
     metric, unit, bound = "longctx_decode_kv_bandwidth", "GB/s", "hbm"
-    launches_per_step = 4  # partial + merge-to-triples (+ all-gather) + merge across ranks
+    launches_per_step = 2  # partial kernel + fused merge / exchange / merge (3 plus the all-gather with --exchange nccl)
     scaling = "strong"
     B, SKV = 8, 131072
     traffic_bytes = None
+    exchange = "peer"
 
     def setup(self, torch, device, seed):
         import torch.distributed as dist
@@ -365,9 +368,17 @@ class LongContextWorkload(Workload):
         g2 = torch.Generator(device=device).manual_seed(seed + 77)
         self.k = torch.randn((self.B, HKV, hi - lo, D), generator=g2, device=device, dtype=torch.bfloat16)
         self.v = torch.randn((self.B, HKV, hi - lo, D), generator=g2, device=device, dtype=torch.bfloat16)
+        self.px = None
+        if self.world > 1 and self.exchange == "peer":
+            self.px = multi_gpu.PeerExchange(self.B * HQ, D, device)
+        else:
+            self.launches_per_step = 3
 
     def step(self):
-        self.out = self.mg.sequence_split_decode(self.q, self.k, self.v)
+        if self.px is not None:
+            self.out = self.px.decode(self.q, self.k, self.v)
+        else:
+            self.out = self.mg.sequence_split_decode(self.q, self.k, self.v)
 
     def work_per_step(self):
         # whole job: all ranks together read the full K and V once
@@ -376,7 +387,9 @@ class LongContextWorkload(Workload):
     def config(self):
         return {"workload": self.name, "batch": self.B, "seq_kv": self.SKV, "heads_q": HQ, "heads_kv": HKV,
                 "head_dim": D, "l2_policy": "inputs larger than L2 (4.3 GB over all ranks)",
-                "sharding": "KV sequence split across ranks; one all-gather of (m, l, O) triples per step"}
+                "sharding": "KV sequence split across ranks; (m, l, O) triples exchanged " +
+                            ("by peer stores inside the merge kernel" if self.px is not None else
+                             "by one NCCL all-gather per step" if self.world > 1 else "locally (one rank)")}
 
     def e2e_setup(self, torch):
         self.hq = self.q.cpu().pin_memory()
@@ -451,6 +464,8 @@ def main():
     ap.add_argument("--workload", default=DEFAULT_WORKLOAD, choices=sorted(WORKLOADS))
     ap.add_argument("--e2e-steps", type=int, default=0, help="0 = min(steps, 5)")
     ap.add_argument("--seed", type=int, default=0)
+    ap.add_argument("--exchange", default="peer", choices=["peer", "nccl"],
+                    help="longctx on more than one GPU: how the triples cross NVLink")
     ap.add_argument("--capture", action="store_true",
                     help="profiler-sized variant of the workload (same kernels, a few hundred MB): flash B=1, "
                          "decode B=16, paged 32 sequences in a 20k-block pool; skips the e2e and CPU legs")
@@ -474,6 +489,7 @@ def main():
     if world > 1:
         dist.init_process_group("nccl", device_id=device)
 
+    LongContextWorkload.exchange = args.exchange
     wl = WORKLOADS[args.workload]()
     if args.capture:
         if isinstance(wl, FlashWorkload):
@@ -575,6 +591,7 @@ def reference_arm(args, rank, world, threads):
         """The CPU arm needs the workload's tensors but no GPU: build them with torch on the host."""
 
     import torch
+    LongContextWorkload.exchange = args.exchange
     wl = WORKLOADS[args.workload]()
     # host tensors with the workload's shapes, reduced to the sample the CPU leg consumes
     g = torch.Generator().manual_seed(args.seed)

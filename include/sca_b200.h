@@ -162,6 +162,43 @@ SCA_ABI int sca_launch_decode_triples(const ScaDecodeFwdParams* params, float* t
 SCA_ABI int sca_launch_merge_triples(const float* gathered, int64_t ranks, int64_t rows,
                                      int64_t head_dim, void* out, int32_t out_dtype, void* stream);
 
+/* Sequence-split decode without a library collective (no counterpart in the reference).
+ *
+ * Every rank creates one exchange buffer (sca_peer_buffer_bytes / _create), hands its 64-byte handle to
+ * the other ranks by any host channel, and maps theirs (_open). sca_launch_seqsplit_exchange then does,
+ * in one kernel: merge of this rank's split-K partials (as written by sca_launch_decode_splitk's partial
+ * kernel: m, l [rows][num_splits], O [rows][num_splits][D], fp32), store of the merged triples into the
+ * buffers of all ranks over NVLink, a bounded wait until all ranks have done the same for `epoch`, and
+ * the final merge into out [rows][D] (same rule as decode_splitk.cu:143-182, applied across ranks).
+ * `epoch` starts at 1 and grows by 1 per call, identically on every rank; calls of one rank must be
+ * ordered (one stream). peer_buffers[rank] is the rank's own buffer. If a peer does not show up within
+ * about a second the kernel gives up, leaves `out` undefined and sets the status word that
+ * sca_peer_exchange_status reads back (0 = all waits were satisfied). One process per GPU: ranks that
+ * share a GPU would wait on kernels that cannot run at the same time. */
+#define SCA_PEER_MAX_RANKS 16
+#define SCA_PEER_HANDLE_BYTES 64
+typedef struct ScaSeqSplitExchange {
+    void* peer_buffers[SCA_PEER_MAX_RANKS];
+    int32_t rank, world;
+    int64_t rows, head_dim, num_splits; /* rows = batch * query heads; head_dim <= 128 */
+    uint32_t epoch;
+    const float* partial_m;
+    const float* partial_l;
+    const float* partial_o;
+    void* out;
+    int32_t out_dtype; /* SCA_DTYPE_* */
+} ScaSeqSplitExchange;
+
+/* the split-K partial kernel alone (fills params->partial_m / _l / _o; `out` is not used) */
+SCA_ABI int sca_launch_decode_partials(const ScaDecodeFwdParams* params, void* stream);
+SCA_ABI long long sca_peer_buffer_bytes(int32_t world, int64_t rows, int64_t head_dim);
+SCA_ABI int sca_peer_buffer_create(int64_t bytes, void** device_ptr, unsigned char* handle_out);
+SCA_ABI int sca_peer_buffer_open(const unsigned char* handle_in, void** device_ptr);
+SCA_ABI int sca_peer_buffer_close(void* device_ptr);   /* a buffer mapped with _open */
+SCA_ABI int sca_peer_buffer_destroy(void* device_ptr); /* a buffer made with _create */
+SCA_ABI int sca_peer_exchange_status(const void* local_buffer, int32_t* status_out);
+SCA_ABI int sca_launch_seqsplit_exchange(const ScaSeqSplitExchange* params, void* stream);
+
 /* Allocation-free split-K decode. No counterpart in the reference.
  *
  * For callers that are not allowed to obtain device memory around the call: code running while a

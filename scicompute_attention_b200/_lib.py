@@ -21,8 +21,13 @@ EXPORTED_SYMBOLS = [
     "sca_flash_smem_bytes_for", "sca_launch_decode_splitk", "sca_launch_decode_splitk_paged",
     "sca_launch_paged_attention", "sca_launch_decode_splitk_static", "sca_launch_decode_triples", "sca_launch_merge_triples",
     "sca_launch_simt_forward", "sca_launch_kv_append", "sca_launch_kv_reset_block",
-    "sca_launch_kv_gather", "sca_launch_kv_append_batched",
+    "sca_launch_kv_gather", "sca_launch_kv_append_batched", "sca_launch_decode_partials",
+    "sca_peer_buffer_bytes", "sca_peer_buffer_create", "sca_peer_buffer_open", "sca_peer_buffer_close",
+    "sca_peer_buffer_destroy", "sca_peer_exchange_status", "sca_launch_seqsplit_exchange",
 ]
+
+PEER_MAX_RANKS = 16
+PEER_HANDLE_BYTES = 64
 
 
 class ScaError(RuntimeError):
@@ -80,6 +85,13 @@ class KvCacheShape(C.Structure):
                 ("head_dim", C.c_int64)]
 
 
+class SeqSplitExchange(C.Structure):
+    _fields_ = [("peer_buffers", C.c_void_p * PEER_MAX_RANKS), ("rank", C.c_int32), ("world", C.c_int32),
+                ("rows", C.c_int64), ("head_dim", C.c_int64), ("num_splits", C.c_int64), ("epoch", C.c_uint32),
+                ("partial_m", C.c_void_p), ("partial_l", C.c_void_p), ("partial_o", C.c_void_p),
+                ("out", C.c_void_p), ("out_dtype", C.c_int32)]
+
+
 _lib = None
 
 
@@ -116,6 +128,15 @@ def lib() -> C.CDLL:
                                             C.POINTER(KvCacheShape), C.c_int64, C.c_void_p]
     l.sca_launch_kv_gather.argtypes = [C.c_void_p, C.c_void_p, C.c_int64, C.c_void_p,
                                        C.POINTER(KvCacheShape), C.c_int64, C.c_void_p]
+    l.sca_launch_decode_partials.argtypes = [C.POINTER(DecodeFwdParams), C.c_void_p]
+    l.sca_peer_buffer_bytes.argtypes = [C.c_int32, C.c_int64, C.c_int64]
+    l.sca_peer_buffer_bytes.restype = C.c_longlong
+    l.sca_peer_buffer_create.argtypes = [C.c_int64, C.POINTER(C.c_void_p), C.c_char_p]
+    l.sca_peer_buffer_open.argtypes = [C.c_char_p, C.POINTER(C.c_void_p)]
+    l.sca_peer_buffer_close.argtypes = [C.c_void_p]
+    l.sca_peer_buffer_destroy.argtypes = [C.c_void_p]
+    l.sca_peer_exchange_status.argtypes = [C.c_void_p, C.POINTER(C.c_int32)]
+    l.sca_launch_seqsplit_exchange.argtypes = [C.POINTER(SeqSplitExchange), C.c_void_p]
     _lib = l
     return l
 

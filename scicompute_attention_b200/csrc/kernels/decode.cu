@@ -592,6 +592,13 @@ extern "C" int sca_launch_paged_attention(const ScaPagedDecodeParams* params, vo
     return sca_launch_decode_splitk_paged(&p, stream);
 }
 
+// Partial kernel only: fills partial_m / partial_l / partial_o; the caller merges (sca_launch_seqsplit_exchange).
+extern "C" int sca_launch_decode_partials(const ScaDecodeFwdParams* params, void* stream) {
+    ClearError();
+    if (int rc = ValidateDecode(params, false)) return rc;
+    return LaunchDecodePartials(*params, static_cast<cudaStream_t>(stream));
+}
+
 extern "C" int sca_launch_decode_triples(const ScaDecodeFwdParams* params, float* triples, void* stream) {
     ClearError();
     if (int rc = ValidateDecode(params, false)) return rc;

@@ -8,8 +8,11 @@ Two schemes, as the workload dictates:
     unnormalised (m, l, O[D]) triple per (batch, head), one small all-gather moves the triples
     (B * H_q * (2 + D) floats per rank), and every rank merges them with the same max-rescaled rule the
     split-K merge kernel uses.
-No kernel here reads a peer's memory; every TMA load is a plain per-CTA load; the only cross-GPU traffic is the
-all-gather.
+Two ways to move the triples: `sequence_split_decode` uses one NCCL all-gather between two kernels;
+`PeerExchange` maps one small buffer per rank into every peer (CUDA IPC) and lets ONE kernel merge the
+local splits, store the triples into all peers over NVLink, wait (bounded) for theirs and do the final
+merge - no library collective on the data path. Every TMA load in the package is a plain per-CTA load of
+local memory; peers are only touched by plain stores from that kernel.
 """
 from __future__ import annotations
 
@@ -78,3 +81,104 @@ def sequence_split_decode(q, k_shard, v_shard, *, group=None, scale=None, num_sp
 
 def shard_sizes(total: int, world: int) -> Sequence[int]:
     return [kv_range_for_rank(total, r, world)[1] - kv_range_for_rank(total, r, world)[0] for r in range(world)]
+
+
+class PeerExchange:
+    """Sequence-split decode whose cross-GPU step is one kernel over peer memory.
+
+    Collective constructor: every rank of `group` builds it with the same (rows = B * H_q, head_dim).
+    It allocates this rank's exchange buffer, all-gathers the 64-byte IPC handles (host side, once) and
+    maps the peers' buffers. `decode` then costs two launches: the split-K partial kernel on this rank's
+    KV shard and the fused merge / exchange / merge kernel. One process per GPU is required.
+    """
+
+    def __init__(self, rows: int, head_dim: int, device, group=None):
+        import ctypes as C
+        import torch
+        import torch.distributed as dist
+        from . import _lib
+        self._lib = _lib
+        self.group = group
+        self.world = dist.get_world_size(group)
+        self.rank = dist.get_rank(group)
+        if self.world > _lib.PEER_MAX_RANKS:
+            raise ValueError(f"at most {_lib.PEER_MAX_RANKS} ranks")
+        self.rows, self.head_dim, self.device = rows, head_dim, torch.device(device)
+        self.epoch = 0
+        l = _lib.lib()
+        nbytes = l.sca_peer_buffer_bytes(self.world, rows, head_dim)
+        if nbytes < 0:
+            raise ValueError("invalid exchange geometry")
+        with torch.cuda.device(self.device):
+            own = C.c_void_p()
+            handle = C.create_string_buffer(_lib.PEER_HANDLE_BYTES)
+            _lib.check(l.sca_peer_buffer_create(nbytes, C.byref(own), handle))
+            self._own = own.value
+            mine = torch.tensor(list(handle.raw), dtype=torch.uint8, device=self.device)
+            everyone = torch.empty((self.world, _lib.PEER_HANDLE_BYTES), dtype=torch.uint8, device=self.device)
+            dist.all_gather_into_tensor(everyone.view(-1), mine, group=group)
+            handles = everyone.cpu().numpy()
+            self._peers = []
+            for r in range(self.world):
+                if r == self.rank:
+                    self._peers.append(self._own)
+                    continue
+                ptr = C.c_void_p()
+                _lib.check(l.sca_peer_buffer_open(bytes(handles[r].tobytes()), C.byref(ptr)))
+                self._peers.append(ptr.value)
+            torch.cuda.synchronize(self.device)
+        dist.barrier(group=group)  # every buffer is zeroed and mapped before the first kernel stores into it
+
+    def decode(self, q, k_shard, v_shard, *, scale=None, num_splits: int = 0, stream=None):
+        """q [B, H_q, 1, D] replicated, k_shard / v_shard [B, H_kv, S_local, D] (S_local may be 0).
+        Returns the normalised output [B * H_q, D] on every rank."""
+        import ctypes as C
+        import torch
+        from . import ops
+        _lib = self._lib
+        b, hq, _, d = q.shape
+        if b * hq != self.rows or d != self.head_dim:
+            raise ValueError("geometry differs from the one the exchange was built for")
+        if k_shard.shape[2] > 0:
+            pm, pl, po, splits = ops.decode_partials(q, k_shard, v_shard, scale=scale, num_splits=num_splits,
+                                                     stream=stream)
+        else:
+            # a rank without tokens contributes m = -inf, l = 0, O = 0 and is skipped by the merge
+            splits = 1
+            ws = torch.zeros(self.rows * (2 + d), dtype=torch.float32, device=q.device)
+            ws[: self.rows] = float("-inf")
+            pm, pl, po = ws[: self.rows], ws[self.rows: 2 * self.rows], ws[2 * self.rows:]
+        out = torch.empty((self.rows, d), dtype=q.dtype, device=q.device)
+        self.epoch += 1
+        x = _lib.SeqSplitExchange()
+        for r, ptr in enumerate(self._peers):
+            x.peer_buffers[r] = ptr
+        x.rank, x.world = self.rank, self.world
+        x.rows, x.head_dim, x.num_splits = self.rows, d, splits
+        x.epoch = self.epoch & 0xFFFFFFFF
+        x.partial_m, x.partial_l, x.partial_o = pm.data_ptr(), pl.data_ptr(), po.data_ptr()
+        x.out, x.out_dtype = out.data_ptr(), ops.dtype_id(q.dtype)
+        _lib.check(_lib.lib().sca_launch_seqsplit_exchange(C.byref(x), ops._stream_ptr(stream)))
+        return out
+
+    def status(self) -> int:
+        """0, or 1 if some launch gave up waiting for a peer (synchronises the device)."""
+        import ctypes as C
+        value = C.c_int32(0)
+        self._lib.check(self._lib.lib().sca_peer_exchange_status(self._own, C.byref(value)))
+        return int(value.value)
+
+    def close(self):
+        """Collective: unmaps the peers' buffers, then frees the own one."""
+        import torch
+        import torch.distributed as dist
+        if self._own is None:
+            return
+        torch.cuda.synchronize(self.device)
+        l = self._lib.lib()
+        for r, ptr in enumerate(self._peers):
+            if r != self.rank:
+                self._lib.check(l.sca_peer_buffer_close(ptr))
+        dist.barrier(group=self.group)  # nobody still maps the buffer that is about to be freed
+        self._lib.check(l.sca_peer_buffer_destroy(self._own))
+        self._own, self._peers = None, []

@@ -235,6 +235,31 @@ def decode_triples(q, k, v, *, scale=None, num_splits: int = 0, stream=None):
     return triples
 
 
+def decode_partials(q, k, v, *, scale=None, num_splits: int = 0, stream=None):
+    """The split-K partial kernel alone. Returns (m [rows, splits], l [rows, splits], O [rows, splits, D],
+    splits) as fp32 views of the scratch pool (valid until the next decode call on this device)."""
+    _require_cuda(q, k, v)
+    b, hq, sq, d = _dims(q, "bhsd")
+    _, hkv, skv, _ = _dims(k, "bhsd")
+    splits = min(num_splits, MAX_SPLITS) if num_splits > 0 else splits_for(skv, b, hkv, hq // hkv, sm_count(q.device))
+    base = b * hq * splits
+    ws = acquire_scratch_fp32(base * (2 + d), q.device)
+    p = DecodeFwdParams()
+    p.q, p.k, p.v, p.out = q.data_ptr(), k.data_ptr(), v.data_ptr(), None
+    p.partial_m = ws.data_ptr()
+    p.partial_l = ws.data_ptr() + 4 * base
+    p.partial_o = ws.data_ptr() + 8 * base
+    p.batch, p.num_heads, p.num_kv_heads, p.seq_kv, p.head_dim, p.num_splits = b, hq, hkv, skv, d, splits
+    p.q_stride = DecodeStrides(*_strides("bhsd", 1, hq, d))
+    p.k_stride = DecodeStrides(*_strides("bhsd", skv, hkv, d))
+    p.v_stride = p.k_stride
+    p.o_stride = DecodeStrides(*_strides("bhsd", 1, hq, d))
+    p.scale = effective_scale(scale, d)
+    p.dtype = dtype_id(q.dtype)
+    check(lib().sca_launch_decode_partials(C.byref(p), _stream_ptr(stream)))
+    return ws[:base], ws[base: 2 * base], ws[2 * base: base * (2 + d)], splits
+
+
 def merge_triples(gathered, out_dtype, *, stream=None):
     """gathered fp32 [ranks, rows, 2 + D] -> normalised output [rows, D] of `out_dtype`."""
     _require_cuda(gathered)

@@ -1,7 +1,9 @@
-"""Sequence-split decode on two real GPUs: each rank runs the CUDA triples operator on its KV slice, NCCL
-all-gathers the triples, each rank merges on the device; the result must match the FP64 oracle on the unsplit
-sequence. In-switch reduction is switched off (NCCL_NVLS_ENABLE=0): the path only needs a plain all-gather.
-Skipped when fewer than two GPUs are visible."""
+"""Sequence-split decode on two real GPUs; the result must match the FP64 oracle on the unsplit sequence.
+Two exchanges are covered: (1) each rank runs the CUDA triples operator on its KV slice, NCCL all-gathers the
+triples, each rank merges on the device; (2) the single kernel that merges, stores the triples into the peer's
+mapped buffer over NVLink, waits (bounded) and merges - several steps in a row, one rank without tokens in one of
+them, and the status word must stay 0. In-switch reduction is switched off (NCCL_NVLS_ENABLE=0); the peer path uses
+plain stores. One process per GPU. Skipped when fewer than two GPUs are visible."""
 import os
 import socket
 import sys
@@ -41,13 +43,33 @@ def _worker(rank, world, port, result_dir):
     torch.cuda.synchronize()
     expect = ol.attention_f64(qd, kd, vd, causal=True)
     H.check_close(H.to_host_f32(out).reshape(b, hq, 1, d), expect, dt, f"sequence-split decode rank {rank}")
+
+    # the same through the peer-memory kernel, three steps with different keys (both buffer halves get reused)
+    px = mg.PeerExchange(b * hq, d, f"cuda:{rank}")
+    for step in range(3):
+        kb2, kd2 = H.normal_inputs((b, hkv, skv, d), 20 + step, dt)
+        k2 = H.to_device(np.ascontiguousarray(kb2[:, :, lo:hi]), dt, f"cuda:{rank}")
+        out2 = px.decode(q, k2, v)
+        torch.cuda.synchronize()
+        H.check_close(H.to_host_f32(out2).reshape(b, hq, 1, d), ol.attention_f64(qd, kd2, vd, causal=True), dt,
+                      f"peer exchange step {step} rank {rank}")
+    # a sequence shorter than the world size leaves the last rank without tokens
+    lo1, hi1 = mg.kv_range_for_rank(1, rank, world)
+    k1 = H.to_device(np.ascontiguousarray(kb[:, :, lo1:hi1]), dt, f"cuda:{rank}")
+    v1 = H.to_device(np.ascontiguousarray(vb[:, :, lo1:hi1]), dt, f"cuda:{rank}")
+    out3 = px.decode(q, k1, v1)
+    torch.cuda.synchronize()
+    H.check_close(H.to_host_f32(out3).reshape(b, hq, 1, d), ol.attention_f64(qd, kd[:, :, :1], vd[:, :, :1], causal=True),
+                  dt, f"peer exchange, one token, rank {rank}")
+    assert px.status() == 0
+    px.close()
     with open(os.path.join(result_dir, f"ok{rank}"), "w") as f:
         f.write("ok")
     dist.barrier()
     dist.destroy_process_group()
 
 
-def test_sequence_split_decode_over_nccl(tmp_path):
+def test_sequence_split_decode_over_nccl_and_over_peer_memory(tmp_path):
     import torch
     import torch.multiprocessing as mp
     if torch.cuda.device_count() < 2:
