@@ -285,7 +285,7 @@ class FlashWorkload(Workload):
     B, S = 4, 4096
     # dram__bytes_read + dram__bytes_write of flash_fwd_sm100_kernel, ncu capture at B=1 scaled x4
     # (profiles/flash_prefill_c2.md); the output mostly stays in L2 until after the kernel
-    traffic_bytes = (50.40e6 + 2.8e6) * 4
+    traffic_bytes = (50.40e6 + 4.1e6) * 4
 
     def setup(self, torch, device, seed):
         from scicompute_attention_b200 import ops

@@ -180,7 +180,7 @@ SCA_ABI int sca_launch_merge_triples(const float* gathered, int64_t ranks, int64
 typedef struct ScaSeqSplitExchange {
     void* peer_buffers[SCA_PEER_MAX_RANKS];
     int32_t rank, world;
-    int64_t rows, head_dim, num_splits; /* rows = batch * query heads; head_dim <= 128 */
+    int64_t rows, head_dim, num_splits; /* rows = batch * query heads; head_dim <= 256 */
     uint32_t epoch;
     const float* partial_m;
     const float* partial_l;

@@ -59,7 +59,7 @@ __device__ __forceinline__ void StoreReleaseSys(unsigned* p, unsigned v) {
 template <typename T>
 __global__ void __launch_bounds__(128)
 seqsplit_exchange_kernel(const ExchangeParams p) {
-    const int d = threadIdx.x;  // one thread per head-dim column (blockDim.x >= head_dim)
+    constexpr int kCols = 2;     // head-dim columns per thread: d = threadIdx.x + 128 c, head_dim <= 256
     const int width = 2 + p.head_dim;
     const size_t half_floats = static_cast<size_t>(p.world) * p.rows * width;
     const size_t slot = (p.epoch & 1u) * half_floats;
@@ -72,19 +72,28 @@ seqsplit_exchange_kernel(const ExchangeParams p) {
         const float* l = p.partial_l + static_cast<size_t>(row) * p.splits;
         float m_all = -CUDART_INF_F;
         for (int s = 0; s < p.splits; ++s) m_all = fmaxf(m_all, m[s]);
-        float l_all = 0.0f, acc = 0.0f;
+        float l_all = 0.0f, acc[kCols] = {0.0f, 0.0f};
         for (int s = 0; s < p.splits; ++s) {
             const float ms = m[s];
             if (ms == -CUDART_INF_F) continue;
             const float wgt = Exp2((ms - m_all) * kLog2e);
             l_all += l[s] * wgt;
-            if (d < p.head_dim) acc += p.partial_o[(static_cast<size_t>(row) * p.splits + s) * p.head_dim + d] * wgt;
+            const float* o = p.partial_o + (static_cast<size_t>(row) * p.splits + s) * p.head_dim;
+#pragma unroll
+            for (int c = 0; c < kCols; ++c) {
+                const int d = threadIdx.x + 128 * c;
+                if (d < p.head_dim) acc[c] += o[d] * wgt;
+            }
         }
         const size_t at = slot + (static_cast<size_t>(p.rank) * p.rows + row) * width;
         for (int r = 0; r < p.world; ++r) {
             float* dst = reinterpret_cast<float*>(p.peer[r] + kHeaderBytes) + at;
-            if (d < p.head_dim) dst[2 + d] = acc;
-            if (d == 0) {
+#pragma unroll
+            for (int c = 0; c < kCols; ++c) {
+                const int d = threadIdx.x + 128 * c;
+                if (d < p.head_dim) dst[2 + d] = acc[c];
+            }
+            if (threadIdx.x == 0) {
                 dst[0] = m_all;
                 dst[1] = l_all;
             }
@@ -130,18 +139,24 @@ seqsplit_exchange_kernel(const ExchangeParams p) {
         for (int s = 0; s < p.world; ++s) {
             m_all = fmaxf(m_all, __ldcg(data + (static_cast<size_t>(s) * p.rows + row) * width));
         }
-        float l_all = 0.0f, acc = 0.0f;
+        float l_all = 0.0f, acc[kCols] = {0.0f, 0.0f};
         for (int s = 0; s < p.world; ++s) {
             const float* t = data + (static_cast<size_t>(s) * p.rows + row) * width;
             const float ms = __ldcg(t);
             if (ms == -CUDART_INF_F) continue;
             const float wgt = Exp2((ms - m_all) * kLog2e);
             l_all += __ldcg(t + 1) * wgt;
-            if (d < p.head_dim) acc += __ldcg(t + 2 + d) * wgt;
+#pragma unroll
+            for (int c = 0; c < kCols; ++c) {
+                const int d = threadIdx.x + 128 * c;
+                if (d < p.head_dim) acc[c] += __ldcg(t + 2 + d) * wgt;
+            }
         }
-        if (d < p.head_dim) {
-            const float inv = l_all > 0.0f ? 1.0f / l_all : 0.0f;
-            reinterpret_cast<T*>(p.out)[static_cast<size_t>(row) * p.head_dim + d] = FromFloat<T>(acc * inv);
+        const float inv = l_all > 0.0f ? 1.0f / l_all : 0.0f;
+#pragma unroll
+        for (int c = 0; c < kCols; ++c) {
+            const int d = threadIdx.x + 128 * c;
+            if (d < p.head_dim) reinterpret_cast<T*>(p.out)[static_cast<size_t>(row) * p.head_dim + d] = FromFloat<T>(acc[c] * inv);
         }
     }
 }
@@ -226,8 +241,8 @@ extern "C" int sca_launch_seqsplit_exchange(const ScaSeqSplitExchange* params, v
         return Fail(SCA_INVALID_ARGUMENT, "sequence-split exchange: rank/world out of range (at most " +
                                               std::to_string(kMaxRanks) + " ranks)");
     }
-    if (x.rows < 1 || x.rows > 0x7fffffffLL || x.head_dim < 1 || x.head_dim > 128 || x.num_splits < 1) {
-        return Fail(SCA_INVALID_ARGUMENT, "sequence-split exchange: rows/head_dim/num_splits out of range (head_dim <= 128)");
+    if (x.rows < 1 || x.rows > 0x7fffffffLL || x.head_dim < 1 || x.head_dim > 256 || x.num_splits < 1) {
+        return Fail(SCA_INVALID_ARGUMENT, "sequence-split exchange: rows/head_dim/num_splits out of range (head_dim <= 256)");
     }
     if (x.partial_m == nullptr || x.partial_l == nullptr || x.partial_o == nullptr || x.out == nullptr) {
         return Fail(SCA_INVALID_ARGUMENT, "sequence-split exchange: null tensor pointer");

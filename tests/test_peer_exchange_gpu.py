@@ -65,6 +65,21 @@ def test_single_rank_exchange_equals_split_k_decode_and_a_missing_peer_times_out
         H.check_close(H.to_host_f32(out).reshape(b, hq, 1, d), expect, dt, f"single-rank exchange, epoch {epoch}")
     assert _status(own) == 0
 
+    # head dims 64 and 256 (two columns per thread at 256)
+    for d2, seed in ((64, 80), (256, 90)):
+        qb2, qd2 = H.normal_inputs((1, 8, 1, d2), seed, ol.DT_BF16)
+        kb2, kd2 = H.normal_inputs((1, 2, 700, d2), seed + 1, ol.DT_BF16)
+        vb2, vd2 = H.normal_inputs((1, 2, 700, d2), seed + 2, ol.DT_BF16)
+        q2, k2, v2 = (H.to_device(x, ol.DT_BF16) for x in (qb2, kb2, vb2))
+        buf = _make_buffer(1, 8, d2)
+        pm, pl, po, splits = ops.decode_partials(q2, k2, v2, num_splits=3)
+        out2 = torch.empty((8, d2), dtype=q2.dtype, device=q2.device)
+        _lib.check(_exchange([buf], 0, 1, 8, d2, splits, 1, pm, pl, po, out2))
+        torch.cuda.synchronize()
+        H.check_close(H.to_host_f32(out2).reshape(1, 8, 1, d2), ol.attention_f64(qd2, kd2, vd2, causal=True), ol.DT_BF16,
+                      f"single-rank exchange D={d2}")
+        _lib.check(_lib.lib().sca_peer_buffer_destroy(buf))
+
     # rank 1 never publishes: the wait is bounded and reports through the status word
     mine, ghost = _make_buffer(2, rows, d), _make_buffer(2, rows, d)
     pm, pl, po, splits = ops.decode_partials(q, k, v, num_splits=4)
