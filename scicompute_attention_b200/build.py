@@ -130,10 +130,27 @@ def build_cpp_tests(force: bool = False, verbose: bool = False) -> str | None:
     return exe
 
 
+def build_examples(force: bool = False, verbose: bool = False) -> str | None:
+    """examples/rollout_engine.cpp -> examples/rollout_engine (public C++ API only)."""
+    src = os.path.join(ROOT, "examples", "rollout_engine.cpp")
+    if not os.path.exists(src) or not os.path.exists(HOST_LIB):
+        return None
+    exe = os.path.join(ROOT, "examples", "rollout_engine")
+    if force or not _newer(exe, [src, HOST_LIB] + _headers()):
+        cxx = shutil.which("g++") or "g++"
+        _run([cxx, "-O2", "-std=c++20", "-Wall", "-I", INCLUDE, "-I", os.path.join(INCLUDE, "sci_infra"), src, "-o", exe,
+              "-L", PKG, "-l:libsci_attention.so", "-l:libsca_b200.so",
+              "-Wl,-rpath,$ORIGIN/../scicompute_attention_b200"])
+    if verbose:
+        print("built", exe)
+    return exe
+
+
 def build_all(force: bool = False, verbose: bool = False) -> None:
     build_kernels(force, verbose)
     build_host(force, verbose)
     build_cpp_tests(force, verbose)
+    build_examples(force, verbose)
 
 
 if __name__ == "__main__":

@@ -70,23 +70,53 @@ SCI_EXPORT std::shared_ptr<CudaDevice> CudaDevice::Create(int device_id) {
     return std::shared_ptr<CudaDevice>(new CudaDevice(device_id, prop.name));
 }
 
+// Tensors come from the device's stream-ordered memory pool (cudaMallocAsync on the legacy default stream)
+// with the pool told to keep what is freed: a call that returns a newly allocated output every time, as the
+// attention entry points do, then costs neither a cudaMalloc nor the device-wide synchronisation of a
+// cudaFree. Frees are ordered on the legacy stream, i.e. after earlier work of every blocking stream.
+// Memory the pool holds counts as used in cudaMemGetInfo until cudaDeviceReset or process exit.
+namespace {
+bool PoolReady(int id) {
+    static std::mutex mu;
+    static std::map<int, bool>* ready = new std::map<int, bool>();
+    std::lock_guard<std::mutex> lock(mu);
+    auto it = ready->find(id);
+    if (it != ready->end()) return it->second;
+    bool ok = false;
+    int supported = 0;
+    cudaMemPool_t pool = nullptr;
+    if (cudaDeviceGetAttribute(&supported, cudaDevAttrMemoryPoolsSupported, id) == cudaSuccess && supported != 0 &&
+        cudaDeviceGetDefaultMemPool(&pool, id) == cudaSuccess) {
+        unsigned long long keep = ~0ull;
+        ok = cudaMemPoolSetAttribute(pool, cudaMemPoolAttrReleaseThreshold, &keep) == cudaSuccess;
+    }
+    if (!ok) cudaGetLastError();
+    (*ready)[id] = ok;
+    return ok;
+}
+}  // namespace
+
 SCI_EXPORT void* CudaDevice::allocate(size_t bytes) {
     void* ptr = nullptr;
+    const size_t n = bytes == 0 ? 1 : bytes;
     WithDevice(id_, [&] {
-        if (cudaMalloc(&ptr, bytes == 0 ? 1 : bytes) != cudaSuccess) {
+        const bool pooled = PoolReady(id_);
+        const cudaError_t got = pooled ? cudaMallocAsync(&ptr, n, cudaStreamLegacy) : cudaMalloc(&ptr, n);
+        if (got != cudaSuccess) {
             cudaGetLastError();
             ptr = nullptr;
             return;
         }
         // fresh tensors read as zero, like the host device's calloc
-        if (cudaMemset(ptr, 0, bytes == 0 ? 1 : bytes) != cudaSuccess) cudaGetLastError();
+        if (cudaMemsetAsync(ptr, 0, n, cudaStreamLegacy) != cudaSuccess) cudaGetLastError();
     });
     return ptr;
 }
 SCI_EXPORT void CudaDevice::deallocate(void* ptr) {
     if (ptr == nullptr) return;
     WithDevice(id_, [&] {
-        if (cudaFree(ptr) != cudaSuccess) cudaGetLastError();
+        const cudaError_t freed = PoolReady(id_) ? cudaFreeAsync(ptr, cudaStreamLegacy) : cudaFree(ptr);
+        if (freed != cudaSuccess) cudaGetLastError();
     });
 }
 SCI_EXPORT void CudaDevice::copy_to_device(void* dst, const void* src, size_t bytes) {

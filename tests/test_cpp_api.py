@@ -32,3 +32,30 @@ def test_every_case_runs_and_passes_on_the_gpu():
     proc, (passed, failed, skipped) = _run()
     assert failed == 0 and proc.returncode == 0, "\n".join(l for l in proc.stdout.splitlines() if "FAIL" in l or "SKIP" in l)[-4000:]
     assert skipped == 0 and passed >= 19
+
+
+ROLLOUT = os.path.join(ROOT, "examples", "rollout_engine")
+
+
+def test_rollout_example_reports_a_missing_gpu_instead_of_crashing():
+    import torch
+    if torch.cuda.is_available():
+        pytest.skip("a GPU is present")
+    if not os.path.exists(ROLLOUT):
+        from scicompute_attention_b200 import build
+        build.build_all()
+    proc = subprocess.run([ROLLOUT, "--requests", "2"], capture_output=True, text=True, timeout=120)
+    assert proc.returncode == 2 and "no CUDA device" in proc.stdout
+
+
+@pytest.mark.gpu
+def test_rollout_example_serves_and_its_two_decode_backends_agree():
+    """Prefill through flash on token-major views, paged caches per layer, batched appends, paged decode; the
+    last step is recomputed by the split-K backend on the gathered cache (--verify)."""
+    if not os.path.exists(ROLLOUT):
+        from scicompute_attention_b200 import build
+        build.build_all()
+    proc = subprocess.run([ROLLOUT, "--requests", "12", "--layers", "2", "--new-tokens", "5", "--prompt-min", "17",
+                           "--prompt-max", "300", "--verify"], capture_output=True, text=True, timeout=600)
+    assert proc.returncode == 0, proc.stdout[-3000:] + proc.stderr[-2000:]
+    assert "verify: paged vs contiguous decode" in proc.stdout and "generated tokens/s" in proc.stdout
