@@ -162,6 +162,29 @@ SCA_ABI int sca_launch_decode_triples(const ScaDecodeFwdParams* params, float* t
 SCA_ABI int sca_launch_merge_triples(const float* gathered, int64_t ranks, int64_t rows,
                                      int64_t head_dim, void* out, int32_t out_dtype, void* stream);
 
+/* Packed variable-length prefill in one launch - replaces the per-sequence launch loop of
+ * FlashBackend::ForwardVarlen (src/backends/flash/flash_backend.cpp:312-363). q / out are packed
+ * [total_q, num_heads, head_dim], k / v [total_kv, num_kv_heads, head_dim]; the offsets are HOST arrays of
+ * num_seqs + 1 int32 (as in the reference API); causal masks are bottom-right aligned per sequence.
+ * `workspace` is device memory of at least sca_flash_varlen_workspace_bytes(num_seqs, total_q) bytes that
+ * must stay untouched until the launch has finished. */
+typedef struct ScaFlashVarlenParams {
+    const void* q;
+    const void* k;
+    const void* v;
+    void* out;
+    int64_t total_q, total_kv, num_heads, num_kv_heads, head_dim, num_seqs;
+    const int32_t* cu_seqlens_q;
+    const int32_t* cu_seqlens_kv;
+    float scale;
+    int32_t causal;
+    int32_t dtype_id;
+    void* workspace;
+    int64_t workspace_bytes;
+} ScaFlashVarlenParams;
+SCA_ABI long long sca_flash_varlen_workspace_bytes(int64_t num_seqs, int64_t total_q);
+SCA_ABI int sca_launch_flash_varlen(const ScaFlashVarlenParams* params, void* stream);
+
 /* Sequence-split decode without a library collective (no counterpart in the reference).
  *
  * Every rank creates one exchange buffer (sca_peer_buffer_bytes / _create), hands its 64-byte handle to

@@ -24,6 +24,7 @@ EXPORTED_SYMBOLS = [
     "sca_launch_kv_gather", "sca_launch_kv_append_batched", "sca_launch_decode_partials",
     "sca_peer_buffer_bytes", "sca_peer_buffer_create", "sca_peer_buffer_open", "sca_peer_buffer_close",
     "sca_peer_buffer_destroy", "sca_peer_exchange_status", "sca_launch_seqsplit_exchange",
+    "sca_flash_varlen_workspace_bytes", "sca_launch_flash_varlen",
 ]
 
 PEER_MAX_RANKS = 16
@@ -85,6 +86,13 @@ class KvCacheShape(C.Structure):
                 ("head_dim", C.c_int64)]
 
 
+class FlashVarlenParams(C.Structure):
+    _fields_ = [("q", C.c_void_p), ("k", C.c_void_p), ("v", C.c_void_p), ("out", C.c_void_p)] + [
+        (n, C.c_int64) for n in ("total_q", "total_kv", "num_heads", "num_kv_heads", "head_dim", "num_seqs")] + [
+        ("cu_seqlens_q", C.c_void_p), ("cu_seqlens_kv", C.c_void_p), ("scale", C.c_float), ("causal", C.c_int32),
+        ("dtype_id", C.c_int32), ("workspace", C.c_void_p), ("workspace_bytes", C.c_int64)]
+
+
 class SeqSplitExchange(C.Structure):
     _fields_ = [("peer_buffers", C.c_void_p * PEER_MAX_RANKS), ("rank", C.c_int32), ("world", C.c_int32),
                 ("rows", C.c_int64), ("head_dim", C.c_int64), ("num_splits", C.c_int64), ("epoch", C.c_uint32),
@@ -128,6 +136,9 @@ def lib() -> C.CDLL:
                                             C.POINTER(KvCacheShape), C.c_int64, C.c_void_p]
     l.sca_launch_kv_gather.argtypes = [C.c_void_p, C.c_void_p, C.c_int64, C.c_void_p,
                                        C.POINTER(KvCacheShape), C.c_int64, C.c_void_p]
+    l.sca_flash_varlen_workspace_bytes.argtypes = [C.c_int64, C.c_int64]
+    l.sca_flash_varlen_workspace_bytes.restype = C.c_longlong
+    l.sca_launch_flash_varlen.argtypes = [C.POINTER(FlashVarlenParams), C.c_void_p]
     l.sca_launch_decode_partials.argtypes = [C.POINTER(DecodeFwdParams), C.c_void_p]
     l.sca_peer_buffer_bytes.argtypes = [C.c_int32, C.c_int64, C.c_int64]
     l.sca_peer_buffer_bytes.restype = C.c_longlong

@@ -410,8 +410,7 @@ public:
         if (result.out.data() == nullptr) {
             return Refuse(AttnStatusCode::kWorkspaceExceeded, "allocation of the varlen output failed");
         }
-        const int64_t esz = DtypeSize(q.dtype());
-        const float scale = EffectiveScale(cfg, probe);
+        // the same per-sequence checks, with the same messages, as the reference's launch loop
         for (int64_t s = 0; s < num_seqs; ++s) {
             const int64_t sq = cu_q[s + 1] - cu_q[s], skv = cu_kv[s + 1] - cu_kv[s];
             if (sq <= 0 || skv <= 0) {
@@ -424,32 +423,38 @@ public:
                                                                   " is causal with S_kv=" + std::to_string(skv) +
                                                                   " < S_q=" + std::to_string(sq));
             }
-            ScaFlashFwdParams p{};
-            p.q = static_cast<const uint8_t*>(q.data()) + cu_q[s] * heads * d * esz;
-            p.k = static_cast<const uint8_t*>(k.data()) + cu_kv[s] * kv_heads * d * esz;
-            p.v = static_cast<const uint8_t*>(v.data()) + cu_kv[s] * kv_heads * d * esz;
-            p.out = static_cast<uint8_t*>(result.out.data()) + cu_q[s] * heads * d * esz;
-            p.batch = 1;
-            p.num_heads = heads;
-            p.num_kv_heads = kv_heads;
-            p.seq_q = sq;
-            p.seq_kv = skv;
-            p.head_dim = d;
-            p.q_sb = sq * heads * d; p.q_sh = d; p.q_ss = heads * d;
-            p.k_sb = skv * kv_heads * d; p.k_sh = d; p.k_ss = kv_heads * d;
-            p.v_sb = p.k_sb; p.v_sh = p.k_sh; p.v_ss = p.k_ss;
-            p.o_sb = p.q_sb; p.o_sh = d; p.o_ss = heads * d;
-            p.scale = scale;
-            p.causal = cfg.causal ? 1 : 0;
-            p.diagonal = cfg.causal ? (skv - sq) : 0;
-            p.dtype_id = DtypeId(q.dtype());
-            if (sci::Status st = FromAbi(sca_launch_flash_fwd(&p, StreamHandle(cfg.stream))); !st.ok()) {
-                return sci::MakeUnexpected<AttentionResult>(st);
-            }
+        }
+        // one launch for the whole batch: the kernel's work list spans all sequences
+        const int64_t ws_bytes = sca_flash_varlen_workspace_bytes(num_seqs, q.dim(0));
+        sci::Tensor workspace(sci::TensorShape({ws_bytes}), sci::DType::kUInt8, q.device());
+        if (workspace.data() == nullptr) {
+            return Refuse(AttnStatusCode::kWorkspaceExceeded, "allocation of the varlen work list failed");
+        }
+        ScaFlashVarlenParams p{};
+        p.q = q.data();
+        p.k = k.data();
+        p.v = v.data();
+        p.out = result.out.data();
+        p.total_q = q.dim(0);
+        p.total_kv = k.dim(0);
+        p.num_heads = heads;
+        p.num_kv_heads = kv_heads;
+        p.head_dim = d;
+        p.num_seqs = num_seqs;
+        p.cu_seqlens_q = cu_q;
+        p.cu_seqlens_kv = cu_kv;
+        p.scale = EffectiveScale(cfg, probe);
+        p.causal = cfg.causal ? 1 : 0;
+        p.dtype_id = DtypeId(q.dtype());
+        p.workspace = workspace.data();
+        p.workspace_bytes = ws_bytes;
+        if (sci::Status st = FromAbi(sca_launch_flash_varlen(&p, StreamHandle(cfg.stream))); !st.ok()) {
+            return sci::MakeUnexpected<AttentionResult>(st);
         }
         result.stats.used_backend = BackendKind::kFlash;
         result.stats.tile = ToTileConfig(*tile);
-        result.stats.note = "varlen: " + std::to_string(num_seqs) + " per-sequence launches over packed buffers (tile " +
+        result.stats.workspace_bytes = static_cast<size_t>(ws_bytes);
+        result.stats.note = "varlen: " + std::to_string(num_seqs) + " sequences in one launch over packed buffers (tile " +
                             tables::FlashTileString(*tile) + ")";
         return sci::Ok(std::move(result));
     }

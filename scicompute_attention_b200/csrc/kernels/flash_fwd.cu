@@ -32,6 +32,7 @@
 #include <algorithm>
 #include <mutex>
 #include <type_traits>
+#include <vector>
 
 #include "common.cuh"
 #include "sm100.cuh"
@@ -88,18 +89,26 @@ struct FlashKernelParams {
     int causal;
     int diagonal;
     int m_blocks;
+    // packed variable-length batches (null for dense [B, H, S, D] problems): seqs[s] = {first query token,
+    // first key token, S_q, S_kv}; entries[e] = {sequence, query block}, heaviest first
+    const int4* seqs;
+    const int2* entries;
+    int num_entries;
 };
 
+// KV tiles a query tile starting at row m0 of its sequence has to visit.
 template <int BN>
-__device__ __forceinline__ int TilesFor(const FlashKernelParams& p, int m0) {
-    if (m0 >= p.seq_q) return 0;
-    int64_t limit = p.seq_kv;
-    if (p.causal) limit = min(limit, static_cast<int64_t>(m0) + kBlockM + p.diagonal);
+__device__ __forceinline__ int TilesFor(int m0, int seq_q, int seq_kv, int causal, int diagonal) {
+    if (m0 >= seq_q) return 0;
+    int64_t limit = seq_kv;
+    if (causal) limit = min(limit, static_cast<int64_t>(m0) + kBlockM + diagonal);
     if (limit <= 0) return 0;
     return static_cast<int>((limit + BN - 1) / BN);
 }
 
-template <typename T, int DP, int QT, int BN>
+// kVarlen: the work list comes from the (sequence, query block) table of a packed ragged batch; otherwise it is
+// computed from the dense [B, H, S, D] geometry and every per-sequence quantity is a launch constant.
+template <typename T, int DP, int QT, int BN, bool kVarlen>
 __global__ void __launch_bounds__(kFlashThreads, 1)
 flash_fwd_sm100_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
                        const __grid_constant__ CUtensorMap map_v, const FlashKernelParams p) {
@@ -134,24 +143,45 @@ flash_fwd_sm100_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
     // the heaviest item of one round gets the lightest of the next (the static schedule then ends within
     // about one KV tile of each other on all SMs). Every role of a CTA walks the same sequence. ----------
     const int bh_count = p.batch * p.heads;
-    const int total_items = p.m_blocks * bh_count;
+    const int total_items = kVarlen ? p.num_entries * p.heads : p.m_blocks * bh_count;
     struct Item {
         int b, h, h_kv;
-        int m0[2];
+        int q_tok0, kv_tok0;          // first row of the sequence in the packed tensors (0 for dense problems)
+        int seq_q, seq_kv, diagonal;  // of this item's sequence
+        int m0[2];                    // first query row of each tile, relative to the sequence
         int ntiles[2];
         int n_max;
     };
     auto decode_item = [&](int idx) {
         Item w;
-        const int mb = p.m_blocks - 1 - idx / bh_count;
-        const int bh = idx % bh_count;
-        w.b = bh / p.heads;
-        w.h = bh % p.heads;
+        int mb;
+        if constexpr (kVarlen) {
+            const int2 entry = __ldg(p.entries + idx / p.heads);
+            const int4 seq = __ldg(p.seqs + entry.x);
+            mb = entry.y;
+            w.b = 0;
+            w.h = idx % p.heads;
+            w.q_tok0 = seq.x;
+            w.kv_tok0 = seq.y;
+            w.seq_q = seq.z;
+            w.seq_kv = seq.w;
+            w.diagonal = p.causal ? seq.w - seq.z : 0;  // bottom-right aligned mask
+        } else {
+            mb = p.m_blocks - 1 - idx / bh_count;
+            const int bh = idx % bh_count;
+            w.b = bh / p.heads;
+            w.h = bh % p.heads;
+            w.q_tok0 = 0;
+            w.kv_tok0 = 0;
+            w.seq_q = p.seq_q;
+            w.seq_kv = p.seq_kv;
+            w.diagonal = p.diagonal;
+        }
         w.h_kv = w.h / (p.heads / p.kv_heads);
         w.m0[0] = (mb * QT) * kBlockM;
         w.m0[1] = (mb * QT + 1) * kBlockM;
-        w.ntiles[0] = TilesFor<BN>(p, w.m0[0]);
-        w.ntiles[1] = QT > 1 ? TilesFor<BN>(p, w.m0[1]) : 0;
+        w.ntiles[0] = TilesFor<BN>(w.m0[0], w.seq_q, w.seq_kv, p.causal, w.diagonal);
+        w.ntiles[1] = QT > 1 ? TilesFor<BN>(w.m0[1], w.seq_q, w.seq_kv, p.causal, w.diagonal) : 0;
         w.n_max = max(w.ntiles[0], w.ntiles[1]);
         return w;
     };
@@ -210,7 +240,7 @@ flash_fwd_sm100_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
                     MbarExpectTx(bar(kQFull + t), G::kQTileBytes);
                     for (int kb = 0; kb < G::kKBlocks; ++kb) {
                         TmaLoad4D(q_smem + t * G::kQTileBytes + kb * G::kQBlockBytes, &map_q, bar(kQFull + t), kb * 64,
-                                  w.m0[t], w.h, w.b);
+                                  w.q_tok0 + w.m0[t], w.h, w.b);
                     }
                     ++q_uses[t];
                 }
@@ -223,7 +253,7 @@ flash_fwd_sm100_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
                     const CUtensorMap* map = (it & 1) ? &map_v : &map_k;
                     for (int kb = 0; kb < G::kKBlocks; ++kb) {
                         TmaLoad4D(ring_smem + slot * G::kKvTileBytes + kb * G::kKvBlockBytes, map, bar(kKvFull + slot),
-                                  kb * 64, (it >> 1) * BN, w.h_kv, w.b);
+                                  kb * 64, w.kv_tok0 + (it >> 1) * BN, w.h_kv, w.b);
                     }
                 }
             }
@@ -354,8 +384,8 @@ flash_fwd_sm100_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
                 // this step has already written. P (16-bit pairs) lands on the first BN / 2 columns of S_t;
                 // the half-row written in step h only covers columns that step h has already consumed.
                 const int col0 = j * BN;
-                const int kv_limit = p.seq_kv - col0;                                   // columns >= kv_limit do not exist
-                const int causal_limit = p.causal ? (row + p.diagonal - col0 + 1) : BN;  // columns >= limit are masked
+                const int kv_limit = w.seq_kv - col0;                                   // columns >= kv_limit do not exist
+                const int causal_limit = p.causal ? (row + w.diagonal - col0 + 1) : BN;  // columns >= limit are masked
                 const int limit = min(kv_limit, causal_limit);
                 const bool ragged = limit < BN;
                 float part4[4] = {0.0f, 0.0f, 0.0f, 0.0f};  // this step's share of the row sum
@@ -453,7 +483,7 @@ flash_fwd_sm100_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
             if (!ok) break;
             TcFenceAfter();
             const float inv = l_sum > 0.0f ? 1.0f / l_sum : 0.0f;
-            T* o_row = reinterpret_cast<T*>(p.out) + w.b * p.o_sb + w.h * p.o_sh + static_cast<int64_t>(row) * p.o_ss;
+            T* o_row = reinterpret_cast<T*>(p.out) + w.b * p.o_sb + w.h * p.o_sh + static_cast<int64_t>(w.q_tok0 + row) * p.o_ss;
 #pragma unroll
             for (int cblk = 0; cblk < DP / 32; ++cblk) {
                 uint32_t r[32];
@@ -463,7 +493,7 @@ flash_fwd_sm100_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
                     TcFenceBefore();
                     MbarArrive(bar(kOFree + t));
                 }
-                if (row < p.seq_q) {
+                if (row < w.seq_q) {
 #pragma unroll
                     for (int v8 = 0; v8 < 4; ++v8) {
                         const int d0 = cblk * 32 + v8 * 8;
@@ -478,7 +508,7 @@ flash_fwd_sm100_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
                     }
                 }
             }
-            if (p.lse != nullptr && row < p.seq_q) {
+            if (p.lse != nullptr && row < w.seq_q) {
                 p.lse[(static_cast<int64_t>(w.b) * p.heads + w.h) * p.seq_q + row] =
                     l_sum > 0.0f ? (m_ref + log2f(l_sum)) * kLn2 : -CUDART_INF_F;
             }
@@ -563,8 +593,68 @@ int* ErrorWordDevicePtr(int** host_view) {
     return dev;
 }
 
+// A packed variable-length batch: host offsets and a device scratch area for the work list.
+struct VarlenWork {
+    const int32_t* cu_q;
+    const int32_t* cu_kv;
+    int64_t num_seqs;
+    void* workspace;
+    int64_t workspace_bytes;
+};
+
+int64_t VarlenWorkspaceBytes(int64_t num_seqs, int64_t total_q) {
+    // one int4 per sequence + one int2 per block of 128 query rows (an upper bound for both geometries)
+    return num_seqs * 16 + (total_q / kBlockM + num_seqs) * 8 + 64;
+}
+
+// Builds {first q token, first kv token, S_q, S_kv} per sequence and the (sequence, query block) list, heaviest
+// block first, and copies both into the workspace (stream-ordered; the host vectors may die on return).
+int UploadVarlenWork(const VarlenWork& vw, int rows_per_entry, int block_n, bool causal, cudaStream_t stream,
+                     const int4** seqs_out, const int2** entries_out, int* num_entries_out) {
+    std::vector<int4> seqs(static_cast<size_t>(vw.num_seqs));
+    struct Weighted {
+        int2 entry;
+        int64_t tiles;
+    };
+    std::vector<Weighted> list;
+    for (int64_t s = 0; s < vw.num_seqs; ++s) {
+        const int64_t sq = static_cast<int64_t>(vw.cu_q[s + 1]) - vw.cu_q[s];
+        const int64_t skv = static_cast<int64_t>(vw.cu_kv[s + 1]) - vw.cu_kv[s];
+        if (sq <= 0 || skv <= 0 || (causal && skv < sq)) {
+            return Fail(SCA_INVALID_ARGUMENT, "flash varlen: sequence " + std::to_string(s) + " has S_q=" + std::to_string(sq) +
+                                                  ", S_kv=" + std::to_string(skv) + (causal ? " (causal needs 0 < S_q <= S_kv)" : " (both must be > 0)"));
+        }
+        seqs[static_cast<size_t>(s)] = make_int4(vw.cu_q[s], vw.cu_kv[s], static_cast<int>(sq), static_cast<int>(skv));
+        for (int64_t mb = 0; mb * rows_per_entry < sq; ++mb) {
+            int64_t limit = skv;
+            if (causal) limit = std::min<int64_t>(limit, std::min<int64_t>(sq, (mb + 1) * rows_per_entry) + (skv - sq));
+            list.push_back({make_int2(static_cast<int>(s), static_cast<int>(mb)), (limit + block_n - 1) / block_n});
+        }
+    }
+    std::stable_sort(list.begin(), list.end(), [](const Weighted& a, const Weighted& b) { return a.tiles > b.tiles; });
+    std::vector<int2> entries(list.size());
+    for (size_t i = 0; i < list.size(); ++i) entries[i] = list[i].entry;
+    const size_t seq_bytes = seqs.size() * sizeof(int4);
+    const size_t entry_bytes = entries.size() * sizeof(int2);
+    if (vw.workspace == nullptr || static_cast<int64_t>(seq_bytes + entry_bytes) > vw.workspace_bytes) {
+        return Fail(SCA_INVALID_ARGUMENT, "flash varlen: workspace of " + std::to_string(vw.workspace_bytes) + " bytes is too small (" +
+                                              std::to_string(seq_bytes + entry_bytes) + " needed)");
+    }
+    unsigned char* base = static_cast<unsigned char*>(vw.workspace);
+    if (cudaError_t e = cudaMemcpyAsync(base, seqs.data(), seq_bytes, cudaMemcpyHostToDevice, stream); e != cudaSuccess) {
+        return FailCuda(e, "cudaMemcpyAsync(varlen sequences)");
+    }
+    if (cudaError_t e = cudaMemcpyAsync(base + seq_bytes, entries.data(), entry_bytes, cudaMemcpyHostToDevice, stream); e != cudaSuccess) {
+        return FailCuda(e, "cudaMemcpyAsync(varlen work list)");
+    }
+    *seqs_out = reinterpret_cast<const int4*>(base);
+    *entries_out = reinterpret_cast<const int2*>(base + seq_bytes);
+    *num_entries_out = static_cast<int>(entries.size());
+    return SCA_OK;
+}
+
 template <typename T, int DP, int QT, int BN>
-int LaunchFlash(const ScaFlashFwdParams& f, float* debug_s, cudaStream_t stream) {
+int LaunchFlash(const ScaFlashFwdParams& f, float* debug_s, cudaStream_t stream, const VarlenWork* varlen = nullptr) {
     using G = FlashGeom<DP, QT, BN>;
     CUtensorMap map_q, map_k, map_v;
     if (int rc = MakeMap(&map_q, f.q, f.dtype_id, f.head_dim, f.seq_q, f.num_heads, f.batch, f.q_ss, f.q_sh, f.q_sb, kBlockM, "q")) return rc;
@@ -596,14 +686,24 @@ int LaunchFlash(const ScaFlashFwdParams& f, float* debug_s, cudaStream_t stream)
     p.causal = f.causal ? 1 : 0;
     p.diagonal = static_cast<int>(f.causal ? f.diagonal : 0);
     p.m_blocks = static_cast<int>((f.seq_q + QT * kBlockM - 1) / (QT * kBlockM));
-    const int64_t ctas = static_cast<int64_t>(p.m_blocks) * p.batch * p.heads;
+    if (varlen != nullptr) {
+        if (int rc = UploadVarlenWork(*varlen, QT * kBlockM, BN, f.causal != 0, stream, &p.seqs, &p.entries, &p.num_entries)) return rc;
+    }
+    const int64_t ctas = varlen != nullptr ? static_cast<int64_t>(p.num_entries) * p.heads
+                                           : static_cast<int64_t>(p.m_blocks) * p.batch * p.heads;
     if (ctas <= 0 || ctas > 0x7fffffffLL) {
         return Fail(SCA_INVALID_ARGUMENT, "flash attention: grid of " + std::to_string(ctas) + " blocks is out of range");
     }
-    const void* fn = reinterpret_cast<const void*>(&flash_fwd_sm100_kernel<T, DP, QT, BN>);
-    if (int rc = EnsureDynamicSmem(fn, G::kSmemBytes, "flash_fwd_sm100_kernel")) return rc;
     const unsigned grid = static_cast<unsigned>(std::min<int64_t>(ctas, SmCount()));  // one persistent CTA per SM
-    flash_fwd_sm100_kernel<T, DP, QT, BN><<<grid, kFlashThreads, G::kSmemBytes, stream>>>(map_q, map_k, map_v, p);
+    if (varlen != nullptr) {
+        const void* fn = reinterpret_cast<const void*>(&flash_fwd_sm100_kernel<T, DP, QT, BN, true>);
+        if (int rc = EnsureDynamicSmem(fn, G::kSmemBytes, "flash_fwd_sm100_kernel")) return rc;
+        flash_fwd_sm100_kernel<T, DP, QT, BN, true><<<grid, kFlashThreads, G::kSmemBytes, stream>>>(map_q, map_k, map_v, p);
+    } else {
+        const void* fn = reinterpret_cast<const void*>(&flash_fwd_sm100_kernel<T, DP, QT, BN, false>);
+        if (int rc = EnsureDynamicSmem(fn, G::kSmemBytes, "flash_fwd_sm100_kernel")) return rc;
+        flash_fwd_sm100_kernel<T, DP, QT, BN, false><<<grid, kFlashThreads, G::kSmemBytes, stream>>>(map_q, map_k, map_v, p);
+    }
     return CheckLaunch("flash_fwd_sm100_kernel", stream);
 }
 
@@ -633,17 +733,17 @@ int ValidateFlash(const ScaFlashFwdParams* params) {
 }
 
 template <typename T>
-int LaunchFlashTyped(const ScaFlashFwdParams& f, float* debug_s, cudaStream_t stream) {
+int LaunchFlashTyped(const ScaFlashFwdParams& f, float* debug_s, cudaStream_t stream, const VarlenWork* varlen = nullptr) {
     // head dims that are not a multiple of 64 run on the next padded geometry: the TMA unit
     // zero-fills the missing columns of Q, K and V, which leaves S and the real columns of O unchanged
     switch (f.head_dim) {
         case 32:
-        case 64: return LaunchFlash<T, 64, 2, 128>(f, debug_s, stream);
+        case 64: return LaunchFlash<T, 64, 2, 128>(f, debug_s, stream, varlen);
         case 96:
-        case 128: return LaunchFlash<T, 128, 2, 128>(f, debug_s, stream);
+        case 128: return LaunchFlash<T, 128, 2, 128>(f, debug_s, stream, varlen);
         case 160:
         case 192:
-        case 256: return LaunchFlash<T, 256, 1, 64>(f, debug_s, stream);
+        case 256: return LaunchFlash<T, 256, 1, 64>(f, debug_s, stream, varlen);
         default: break;
     }
     return Fail(SCA_INVALID_ARGUMENT, "flash attention: head_dim=" + std::to_string(f.head_dim) + " is not instantiated");
@@ -678,4 +778,55 @@ extern "C" int sca_launch_flash_fwd(const ScaFlashFwdParams* params, void* strea
     cudaStream_t s = static_cast<cudaStream_t>(stream);
     return params->dtype_id == SCA_DTYPE_F16 ? LaunchFlashTyped<__half>(*params, nullptr, s)
                                              : LaunchFlashTyped<__nv_bfloat16>(*params, nullptr, s);
+}
+
+extern "C" long long sca_flash_varlen_workspace_bytes(int64_t num_seqs, int64_t total_q) {
+    if (num_seqs < 1 || total_q < 1) return -1;
+    return VarlenWorkspaceBytes(num_seqs, total_q);
+}
+
+// Packed variable-length prefill in ONE launch (the reference loops over the sequences on the host,
+// src/backends/flash/flash_backend.cpp:312-363): the persistent kernel's work list simply spans all sequences.
+extern "C" int sca_launch_flash_varlen(const ScaFlashVarlenParams* params, void* stream) {
+    ClearError();
+    if (params == nullptr || params->cu_seqlens_q == nullptr || params->cu_seqlens_kv == nullptr) {
+        return Fail(SCA_INVALID_ARGUMENT, "flash varlen: null parameter block or host offsets");
+    }
+    const ScaFlashVarlenParams& x = *params;
+    if (x.num_seqs < 1 || x.total_q < 1 || x.total_kv < 1) return Fail(SCA_INVALID_ARGUMENT, "flash varlen: empty batch");
+    if (x.cu_seqlens_q[0] != 0 || x.cu_seqlens_kv[0] != 0 || x.cu_seqlens_q[x.num_seqs] != x.total_q ||
+        x.cu_seqlens_kv[x.num_seqs] != x.total_kv) {
+        return Fail(SCA_INVALID_ARGUMENT, "flash varlen: offsets must start at 0 and end at the token totals");
+    }
+    ScaFlashFwdParams f{};
+    f.q = x.q;
+    f.k = x.k;
+    f.v = x.v;
+    f.out = x.out;
+    f.batch = 1;
+    f.num_heads = x.num_heads;
+    f.num_kv_heads = x.num_kv_heads;
+    f.seq_q = x.total_q;
+    f.seq_kv = x.total_kv;
+    f.head_dim = x.head_dim;
+    f.q_ss = x.num_heads * x.head_dim;
+    f.q_sh = x.head_dim;
+    f.q_sb = x.total_q * f.q_ss;
+    f.k_ss = x.num_kv_heads * x.head_dim;
+    f.k_sh = x.head_dim;
+    f.k_sb = x.total_kv * f.k_ss;
+    f.v_ss = f.k_ss;
+    f.v_sh = f.k_sh;
+    f.v_sb = f.k_sb;
+    f.o_ss = f.q_ss;
+    f.o_sh = f.q_sh;
+    f.o_sb = f.q_sb;
+    f.scale = x.scale;
+    f.causal = x.causal;
+    f.dtype_id = x.dtype_id;
+    if (int rc = ValidateFlash(&f)) return rc;
+    VarlenWork vw{x.cu_seqlens_q, x.cu_seqlens_kv, x.num_seqs, x.workspace, x.workspace_bytes};
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    return f.dtype_id == SCA_DTYPE_F16 ? LaunchFlashTyped<__half>(f, nullptr, s, &vw)
+                                       : LaunchFlashTyped<__nv_bfloat16>(f, nullptr, s, &vw);
 }

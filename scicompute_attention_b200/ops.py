@@ -318,6 +318,37 @@ def flash_attention(q, k, v, *, causal=False, scale=None, return_lse=False, layo
     return (out, lse) if return_lse else out
 
 
+def flash_attention_varlen(q, k, v, cu_seqlens_q, cu_seqlens_kv, *, causal=False, scale=None, stream=None):
+    """Packed variable-length prefill in one launch. q [T_q, H_q, D], k / v [T_kv, H_kv, D] on the device;
+    cu_seqlens_* are HOST int32 offsets (num_seqs + 1 entries, as in the reference API). Returns [T_q, H_q, D]."""
+    import numpy as np
+    _require_cuda(q, k, v)
+    if q.dim() != 3 or k.dim() != 3 or tuple(k.shape) != tuple(v.shape) or not (q.is_contiguous() and k.is_contiguous() and v.is_contiguous()):
+        raise _lib.ScaError(4, "varlen expects contiguous packed [T, H, D] tensors")
+    cu_q = np.ascontiguousarray(cu_seqlens_q, dtype=np.int32)
+    cu_kv = np.ascontiguousarray(cu_seqlens_kv, dtype=np.int32)
+    if cu_q.ndim != 1 or cu_q.shape != cu_kv.shape or cu_q.shape[0] < 2:
+        raise _lib.ScaError(4, "cu_seqlens_q / cu_seqlens_kv must be host int32 arrays of num_seqs + 1 entries")
+    tq, hq, d = q.shape
+    tkv, hkv, _ = k.shape
+    n = cu_q.shape[0] - 1
+    out = torch.empty_like(q)
+    ws_bytes = lib().sca_flash_varlen_workspace_bytes(n, tq)
+    ws = torch.empty(max(int(ws_bytes), 16), dtype=torch.uint8, device=q.device)
+    p = _lib.FlashVarlenParams()
+    p.q, p.k, p.v, p.out = q.data_ptr(), k.data_ptr(), v.data_ptr(), out.data_ptr()
+    p.total_q, p.total_kv, p.num_heads, p.num_kv_heads, p.head_dim, p.num_seqs = tq, tkv, hq, hkv, d, n
+    p.cu_seqlens_q, p.cu_seqlens_kv = cu_q.ctypes.data, cu_kv.ctypes.data
+    p.scale = effective_scale(scale, d)
+    p.causal = 1 if causal else 0
+    p.dtype_id = dtype_id(q.dtype)
+    p.workspace, p.workspace_bytes = ws.data_ptr(), ws.numel()
+    check(lib().sca_launch_flash_varlen(C.byref(p), _stream_ptr(stream)))
+    if stream is None:
+        ws.record_stream(torch.cuda.current_stream(q.device))
+    return out
+
+
 def simt_attention(q, k, v, *, causal=False, scale=None, return_lse=False, layout="bhsd", stream=None):
     """Functional SIMT attention behind the naive / tiled backends (any compute dtype)."""
     _require_cuda(q, k, v)

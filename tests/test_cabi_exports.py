@@ -34,6 +34,8 @@ def test_struct_sizes_match_header_layout():
     assert C.sizeof(_lib.DecodeFwdParams) == 7 * 8 + 6 * 8 + 4 * 24 + 8 + 8 + 3 * 8 + 8
     assert C.sizeof(_lib.FlashFwdParams) == 5 * 8 + 18 * 8 + 16 + 8 + 8
     assert C.sizeof(_lib.PagedDecodeParams) == C.sizeof(_lib.DecodeFwdParams) + 32
+    assert C.sizeof(_lib.FlashVarlenParams) == 4 * 8 + 6 * 8 + 2 * 8 + 4 + 4 + 4 + 4 + 8 + 8
+    assert C.sizeof(_lib.SeqSplitExchange) == 16 * 8 + 8 + 3 * 8 + 8 + 3 * 8 + 8 + 8
 
 
 def test_null_arguments_are_invalid_argument_not_a_crash():
@@ -73,3 +75,22 @@ def test_python_ops_refuse_cpu_tensors():
     with pytest.raises(_lib.ScaError) as e:
         ops.decode_attention(q, k, k)
     assert "no CPU path" in str(e.value)
+
+
+def test_new_entry_points_validate_before_touching_the_device():
+    import numpy as np
+    lib = _lib.lib()
+    assert lib.sca_launch_flash_varlen(None, None) == 4
+    p = _lib.FlashVarlenParams()
+    cu = np.array([0, 5, 9], dtype=np.int32)
+    p.cu_seqlens_q, p.cu_seqlens_kv = cu.ctypes.data, cu.ctypes.data
+    p.num_seqs, p.total_q, p.total_kv = 2, 10, 9   # offsets end at 9, total_q says 10
+    assert lib.sca_launch_flash_varlen(C.byref(p), None) == 4
+    assert b"offsets" in lib.sca_last_error()
+    assert lib.sca_flash_varlen_workspace_bytes(0, 10) == -1 and lib.sca_flash_varlen_workspace_bytes(3, 1000) > 3 * 16
+    assert lib.sca_launch_seqsplit_exchange(None, None) == 4
+    x = _lib.SeqSplitExchange()
+    x.rank, x.world = 2, 2
+    assert lib.sca_launch_seqsplit_exchange(C.byref(x), None) == 4 and b"rank" in lib.sca_last_error()
+    assert lib.sca_peer_buffer_bytes(2, 256, 128) == 512 + 2 * 2 * 256 * 130 * 4
+    assert lib.sca_launch_decode_partials(None, None) == 4

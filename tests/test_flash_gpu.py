@@ -119,3 +119,46 @@ def test_simt_reference_backend_matches_oracle_including_fp32():
         expect, elog = ol.attention_f64(qd, kd, vd, causal=causal, want_lse=True)
         H.check_close(H.to_host_f32(out), expect, dt, f"simt dt={dt}")
         assert np.abs(lse.cpu().numpy() - elog).max() <= 1e-3
+
+
+def test_packed_variable_length_batches_in_one_launch():
+    """Ragged batches through sca_launch_flash_varlen: every sequence must equal the oracle on that sequence alone
+    (rows of a neighbouring sequence that a tile load drags in must not leak into the result)."""
+    import torch
+    from scicompute_attention_b200 import ops
+    cases = [
+        (ol.DT_F16, 128, 8, 2, True, [1, 63, 128, 129, 300, 17, 1000], None),
+        (ol.DT_BF16, 128, 32, 8, True, [512, 5, 256, 257], None),
+        (ol.DT_F16, 64, 4, 4, False, [40, 256, 3, 700], [90, 256, 64, 701]),
+        (ol.DT_BF16, 256, 4, 2, True, [130, 64, 1, 250], [200, 64, 5, 250]),
+        (ol.DT_F16, 96, 6, 3, True, [77, 200], None),
+    ]
+    seed = 69000
+    for dt, d, hq, hkv, causal, q_lens, kv_lens in cases:
+        kv_lens = kv_lens or q_lens
+        cu_q = np.concatenate([[0], np.cumsum(q_lens)]).astype(np.int32)
+        cu_kv = np.concatenate([[0], np.cumsum(kv_lens)]).astype(np.int32)
+        # unit-variance logits; V uniform in [-1, 1] so that |out| < 1 and the bf16 output rounding (half an ulp is
+        # 7.8e-3 in [2, 4)) cannot reach the 8e-3 bound by itself
+        qb, qd = H.normal_inputs((int(cu_q[-1]), hq, d), seed, dt)
+        kb, kd = H.normal_inputs((int(cu_kv[-1]), hkv, d), seed + 1, dt)
+        vb, vd = H.uniform_inputs((int(cu_kv[-1]), hkv, d), seed + 2, dt)
+        out = ops.flash_attention_varlen(H.to_device(qb, dt), H.to_device(kb, dt), H.to_device(vb, dt), cu_q, cu_kv,
+                                         causal=causal)
+        torch.cuda.synchronize()
+        got = H.to_host_f32(out)
+        for s in range(len(q_lens)):
+            qs = qd[cu_q[s]:cu_q[s + 1]].transpose(1, 0, 2)[None]
+            ks = kd[cu_kv[s]:cu_kv[s + 1]].transpose(1, 0, 2)[None]
+            vs = vd[cu_kv[s]:cu_kv[s + 1]].transpose(1, 0, 2)[None]
+            expect = ol.attention_f64(qs, ks, vs, causal=causal)
+            H.check_close(got[cu_q[s]:cu_q[s + 1]].transpose(1, 0, 2)[None], expect, dt,
+                          f"varlen dt={dt} D={d} seq {s} S_q={q_lens[s]} S_kv={kv_lens[s]} causal={causal}")
+        seed += 10
+    # argument checks: a causal sequence with fewer keys than queries, and offsets that do not end at the totals
+    q = torch.zeros(8, 2, 64, dtype=torch.float16, device="cuda")
+    from scicompute_attention_b200 import _lib
+    with pytest.raises(_lib.ScaError):
+        ops.flash_attention_varlen(q, q[:6].contiguous(), q[:6].contiguous(), [0, 8], [0, 6], causal=True)
+    with pytest.raises(_lib.ScaError):
+        ops.flash_attention_varlen(q, q, q, [0, 7], [0, 8])
