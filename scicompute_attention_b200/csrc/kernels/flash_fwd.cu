@@ -23,6 +23,9 @@
 //     absorbs the stale reference point exactly;
 //   * tensor memory: S_0 | S_1 | O_0 | O_1, 128 (or D) fp32 columns each, 512 columns in total.
 //
+// Packed variable-length batches run on the same kernel: the work list then holds (sequence, query block)
+// entries and every item carries its sequence's lengths and token offsets (see sca_launch_flash_varlen).
+//
 // Every wait on an mbarrier is bounded (sm100.cuh): on expiry the role raises a CTA-wide abort flag,
 // the kernel records a code in a host-visible word, frees its tensor memory and returns.
 //
