@@ -84,7 +84,6 @@ struct FlashGeom {
 struct FlashKernelParams {
     void* out;
     float* lse;
-    float* debug_s;  // optional: raw S of the first KV tile, [ctas][2][128][128] fp32 (tests only)
     int* error_word; // host-visible; non-zero after a wait expired
     int seq_q, seq_kv, heads, kv_heads, head_dim, batch;
     int64_t o_sb, o_sh, o_ss;
@@ -398,14 +397,6 @@ flash_fwd_sm100_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
                     TmemLd32(s_addr + half * 64, ra);
                     TmemLd32(s_addr + half * 64 + 32, rb);
                     TmemWaitLd();
-                    if (p.debug_s != nullptr && j == 0) {
-                        float* dst = p.debug_s + ((static_cast<size_t>(idx) * 2 + t) * kBlockM + row_in_tile) * 128 + half * 64;
-    #pragma unroll
-                        for (int i = 0; i < 32; ++i) {
-                            dst[i] = __uint_as_float(ra[i]);
-                            dst[32 + i] = __uint_as_float(rb[i]);
-                        }
-                    }
                     if (ragged) {
     #pragma unroll
                         for (int i = 0; i < 32; ++i) {
@@ -657,7 +648,7 @@ int UploadVarlenWork(const VarlenWork& vw, int rows_per_entry, int block_n, bool
 }
 
 template <typename T, int DP, int QT, int BN>
-int LaunchFlash(const ScaFlashFwdParams& f, float* debug_s, cudaStream_t stream, const VarlenWork* varlen = nullptr) {
+int LaunchFlash(const ScaFlashFwdParams& f, cudaStream_t stream, const VarlenWork* varlen = nullptr) {
     using G = FlashGeom<DP, QT, BN>;
     CUtensorMap map_q, map_k, map_v;
     if (int rc = MakeMap(&map_q, f.q, f.dtype_id, f.head_dim, f.seq_q, f.num_heads, f.batch, f.q_ss, f.q_sh, f.q_sb, kBlockM, "q")) return rc;
@@ -667,7 +658,6 @@ int LaunchFlash(const ScaFlashFwdParams& f, float* debug_s, cudaStream_t stream,
     FlashKernelParams p{};
     p.out = f.out;
     p.lse = f.return_lse ? f.lse : nullptr;
-    p.debug_s = debug_s;
     int* host_word = nullptr;
     p.error_word = ErrorWordDevicePtr(&host_word);
     if (host_word != nullptr && *host_word != 0) {
@@ -736,17 +726,17 @@ int ValidateFlash(const ScaFlashFwdParams* params) {
 }
 
 template <typename T>
-int LaunchFlashTyped(const ScaFlashFwdParams& f, float* debug_s, cudaStream_t stream, const VarlenWork* varlen = nullptr) {
+int LaunchFlashTyped(const ScaFlashFwdParams& f, cudaStream_t stream, const VarlenWork* varlen = nullptr) {
     // head dims that are not a multiple of 64 run on the next padded geometry: the TMA unit
     // zero-fills the missing columns of Q, K and V, which leaves S and the real columns of O unchanged
     switch (f.head_dim) {
         case 32:
-        case 64: return LaunchFlash<T, 64, 2, 128>(f, debug_s, stream, varlen);
+        case 64: return LaunchFlash<T, 64, 2, 128>(f, stream, varlen);
         case 96:
-        case 128: return LaunchFlash<T, 128, 2, 128>(f, debug_s, stream, varlen);
+        case 128: return LaunchFlash<T, 128, 2, 128>(f, stream, varlen);
         case 160:
         case 192:
-        case 256: return LaunchFlash<T, 256, 1, 64>(f, debug_s, stream, varlen);
+        case 256: return LaunchFlash<T, 256, 1, 64>(f, stream, varlen);
         default: break;
     }
     return Fail(SCA_INVALID_ARGUMENT, "flash attention: head_dim=" + std::to_string(f.head_dim) + " is not instantiated");
@@ -765,22 +755,12 @@ extern "C" long long sca_flash_smem_bytes_for(int head_dim, long long elem_bytes
     return q + 2 * kv + 1024;
 }
 
-// Test hook (not declared in the public header): same launch with a raw-S dump of the first KV tile.
-extern "C" __attribute__((visibility("default"))) int sca_debug_flash_fwd(const ScaFlashFwdParams* params,
-                                                                          float* debug_s, void* stream) {
-    ClearError();
-    if (int rc = ValidateFlash(params)) return rc;
-    cudaStream_t s = static_cast<cudaStream_t>(stream);
-    return params->dtype_id == SCA_DTYPE_F16 ? LaunchFlashTyped<__half>(*params, debug_s, s)
-                                             : LaunchFlashTyped<__nv_bfloat16>(*params, debug_s, s);
-}
-
 extern "C" int sca_launch_flash_fwd(const ScaFlashFwdParams* params, void* stream) {
     ClearError();
     if (int rc = ValidateFlash(params)) return rc;
     cudaStream_t s = static_cast<cudaStream_t>(stream);
-    return params->dtype_id == SCA_DTYPE_F16 ? LaunchFlashTyped<__half>(*params, nullptr, s)
-                                             : LaunchFlashTyped<__nv_bfloat16>(*params, nullptr, s);
+    return params->dtype_id == SCA_DTYPE_F16 ? LaunchFlashTyped<__half>(*params, s)
+                                             : LaunchFlashTyped<__nv_bfloat16>(*params, s);
 }
 
 extern "C" long long sca_flash_varlen_workspace_bytes(int64_t num_seqs, int64_t total_q) {
@@ -830,6 +810,6 @@ extern "C" int sca_launch_flash_varlen(const ScaFlashVarlenParams* params, void*
     if (int rc = ValidateFlash(&f)) return rc;
     VarlenWork vw{x.cu_seqlens_q, x.cu_seqlens_kv, x.num_seqs, x.workspace, x.workspace_bytes};
     cudaStream_t s = static_cast<cudaStream_t>(stream);
-    return f.dtype_id == SCA_DTYPE_F16 ? LaunchFlashTyped<__half>(f, nullptr, s, &vw)
-                                       : LaunchFlashTyped<__nv_bfloat16>(f, nullptr, s, &vw);
+    return f.dtype_id == SCA_DTYPE_F16 ? LaunchFlashTyped<__half>(f, s, &vw)
+                                       : LaunchFlashTyped<__nv_bfloat16>(f, s, &vw);
 }
