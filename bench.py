@@ -286,14 +286,16 @@ class FlashWorkload(Workload):
     # dram__bytes_read + dram__bytes_write of flash_fwd_sm100_kernel, ncu capture at B=1 scaled x4
     # (profiles/flash_prefill_c2.md); the output mostly stays in L2 until after the kernel
     traffic_bytes = (50.40e6 + 4.1e6) * 4
+    dtype_name = "bf16"  # --dtype fp16 runs the same configuration in half precision
 
     def setup(self, torch, device, seed):
         from scicompute_attention_b200 import ops
         self.torch, self.ops = torch, ops
         g = torch.Generator(device=device).manual_seed(seed)
-        self.q = torch.randn((self.B, HQ, self.S, D), generator=g, device=device, dtype=torch.bfloat16)
-        self.k = torch.randn((self.B, HKV, self.S, D), generator=g, device=device, dtype=torch.bfloat16)
-        self.v = torch.randn((self.B, HKV, self.S, D), generator=g, device=device, dtype=torch.bfloat16)
+        dt = torch.float16 if self.dtype_name == "fp16" else torch.bfloat16
+        self.q = torch.randn((self.B, HQ, self.S, D), generator=g, device=device, dtype=torch.float32).to(dt)
+        self.k = torch.randn((self.B, HKV, self.S, D), generator=g, device=device, dtype=torch.float32).to(dt)
+        self.v = torch.randn((self.B, HKV, self.S, D), generator=g, device=device, dtype=torch.float32).to(dt)
         self.out = torch.empty_like(self.q)
         # 256 MiB scratch written between steps would flush L2; inputs + output (320 MiB) already exceed it
         self.flush = None
@@ -305,8 +307,8 @@ class FlashWorkload(Workload):
         return 4 * self.B * HQ * D * (self.S * (self.S + 1) // 2)
 
     def config(self):
-        return {"workload": self.name, "batch": self.B, "seq_len": self.S, "heads_q": HQ, "heads_kv": HKV,
-                "head_dim": D, "causal": True,
+        return {"workload": self.name.replace("bf16", self.dtype_name), "batch": self.B, "seq_len": self.S, "heads_q": HQ,
+                "heads_kv": HKV, "head_dim": D, "causal": True,
                 "l2_policy": "inputs + output (335 MB per step) larger than L2",
                 "sharding": "independent (batch, kv-head group) units per GPU, no collective"}
 
@@ -314,7 +316,7 @@ class FlashWorkload(Workload):
         self.hq = self.q.cpu().pin_memory()
         self.hk = self.k.cpu().pin_memory()
         self.hv = self.v.cpu().pin_memory()
-        self.ho = torch.empty(self.q.shape, dtype=torch.bfloat16).pin_memory()
+        self.ho = torch.empty(self.q.shape, dtype=self.q.dtype).pin_memory()
         self.h2d = (self.hq.numel() + self.hk.numel() + self.hv.numel()) * 2
         self.d2h = self.ho.numel() * 2
         self.e2e_streams = [torch.cuda.Stream() for _ in range(self.B)]
@@ -477,6 +479,7 @@ def main():
     ap.add_argument("--workload", default=DEFAULT_WORKLOAD, choices=sorted(WORKLOADS))
     ap.add_argument("--e2e-steps", type=int, default=0, help="0 = min(steps, 5)")
     ap.add_argument("--seed", type=int, default=0)
+    ap.add_argument("--dtype", default="bf16", choices=["bf16", "fp16"], help="flash workload only")
     ap.add_argument("--exchange", default="peer", choices=["peer", "nccl"],
                     help="longctx on more than one GPU: how the triples cross NVLink")
     ap.add_argument("--capture", action="store_true",
@@ -503,6 +506,7 @@ def main():
         dist.init_process_group("nccl", device_id=device)
 
     LongContextWorkload.exchange = args.exchange
+    FlashWorkload.dtype_name = args.dtype
     wl = WORKLOADS[args.workload]()
     if args.capture:
         if isinstance(wl, FlashWorkload):
@@ -575,7 +579,8 @@ def main():
         line = {
             "metric": wl.metric, "value": value, "unit": wl.unit, "n_gpus": world, "steps": args.steps,
             "warmup": args.warmup, "ms_per_step": ms_step, "higher_is_better": True, "scaling": getattr(wl, "scaling", "weak"),
-            "vs_baseline": None, "dtype": "bf16", "data": "synthetic (seeded iid N(0,1), random page tables)",
+            "vs_baseline": None, "dtype": getattr(wl, "dtype_name", "bf16"),
+            "data": "synthetic (seeded iid N(0,1), random page tables)",
             "config": wl.config(),
             "roofline": {"bound": wl.bound, "achieved": per_gpu, "peak": peak, "unit": wl.unit,
                          "frac": per_gpu / peak, "peak_source": peaks["source"],
@@ -605,6 +610,7 @@ def reference_arm(args, rank, world, threads):
 
     import torch
     LongContextWorkload.exchange = args.exchange
+    FlashWorkload.dtype_name = args.dtype
     wl = WORKLOADS[args.workload]()
     # host tensors with the workload's shapes, reduced to the sample the CPU leg consumes
     g = torch.Generator().manual_seed(args.seed)
