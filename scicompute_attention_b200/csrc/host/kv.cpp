@@ -206,8 +206,9 @@ sci::Result<KVCache> KVCache::Create(const KVCacheConfig& cfg, sci::Device& devi
     if (!bytes.ok()) return sci::MakeUnexpected<KVCache>(bytes.error());
 
     // an over-budget request is answered with an error code and a suggestion, never with an OOM
-    unsigned long long free_b = 0, total_b = 0;
-    if (device.type() == sci::DeviceType::kCUDA && sca_mem_get_info(&free_b, &total_b) == 0) {
+    // "free" counts what the tensor pool holds without using it: the cache is allocated from that pool
+    const unsigned long long free_b = device.type() == sci::DeviceType::kCUDA ? device.free_memory() : 0;
+    if (device.type() == sci::DeviceType::kCUDA && free_b > 0) {
         const double budget = static_cast<double>(free_b) * kKvBudgetRatio;
         if (static_cast<double>(*bytes) > budget) {
             const int64_t fit = MaxBlocksForBudget(cfg, static_cast<size_t>(budget / (2 * cfg.num_layers)));

@@ -146,7 +146,21 @@ SCI_EXPORT size_t CudaDevice::total_memory() const {
 }
 SCI_EXPORT size_t CudaDevice::free_memory() const {
     size_t free_b = 0, total_b = 0;
-    WithDevice(id_, [&] { cudaMemGetInfo(&free_b, &total_b); });
+    WithDevice(id_, [&] {
+        cudaMemGetInfo(&free_b, &total_b);
+        // what the tensor pool holds but does not use is available to the next tensor
+        if (PoolReady(id_)) {
+            cudaMemPool_t pool = nullptr;
+            unsigned long long reserved = 0, used = 0;
+            if (cudaDeviceGetDefaultMemPool(&pool, id_) == cudaSuccess &&
+                cudaMemPoolGetAttribute(pool, cudaMemPoolAttrReservedMemCurrent, &reserved) == cudaSuccess &&
+                cudaMemPoolGetAttribute(pool, cudaMemPoolAttrUsedMemCurrent, &used) == cudaSuccess && reserved > used) {
+                free_b += static_cast<size_t>(reserved - used);
+            } else {
+                cudaGetLastError();
+            }
+        }
+    });
     return free_b;
 }
 
