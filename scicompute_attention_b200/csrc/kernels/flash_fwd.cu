@@ -21,7 +21,10 @@
 //     values. The reference point moves (and O, the sum and the part of P already written are
 //     rescaled) only when a half-row exceeds it by more than 2^8; the final division by the row sum
 //     absorbs the stale reference point exactly;
-//   * tensor memory: S_0 | S_1 | O_0 | O_1, 128 (or D) fp32 columns each, 512 columns in total.
+//   * tensor memory: S_0 | S_1 | O_0 | O_1, 128 (or D) fp32 columns each, 512 columns in total;
+//   * head dims above 128 leave room for one query tile only (O needs 256 columns). There the scores of
+//     64-key tiles are double-buffered instead: S(j+1) is computed while the softmax of tile j runs, and
+//     S(j+2) follows P(j) V_j into the buffer P(j) came from.
 //
 // Packed variable-length batches run on the same kernel: the work list then holds (sequence, query block)
 // entries and every item carries its sequence's lengths and token offsets (see sca_launch_flash_varlen).
@@ -71,7 +74,7 @@ struct FlashGeom {
     static constexpr int kKvBlockBytes = BN * 128;          // one column block of a K or V tile
     static constexpr int kQTileBytes = kKBlocks * kQBlockBytes;
     static constexpr int kKvTileBytes = kKBlocks * kKvBlockBytes;
-    static constexpr int kSlots = (DP == 128) ? 5 : (DP == 64 ? 8 : 4);  // K/V ring
+    static constexpr int kSlots = (DP == 64) ? 8 : 5;  // K/V ring
     static constexpr int kBarrierBytes = 256;
     static constexpr int kSmemBytes = 1024 + QT * kQTileBytes + kSlots * kKvTileBytes + kBarrierBytes;
     static constexpr int kSCol = 0;                         // S_t at kSCol + t * 128
@@ -137,6 +140,10 @@ flash_fwd_sm100_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(smem + (bar_base - smem_base) + kNumBars * 8);
     volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
+    // One query tile per CTA (head dims above 128): no second tile to ping-pong with, so the scores are double-
+    // buffered instead: S(j+1) is computed while the softmax of block j runs. The barriers s_full / p_full / o_done
+    // are then indexed by the score buffer j & 1 instead of by the query tile.
+    constexpr bool kDoubleS = (QT == 1);
     const int warp = threadIdx.x >> 5;
     const int lane = threadIdx.x & 31;
 
@@ -246,16 +253,35 @@ flash_fwd_sm100_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
                     }
                     ++q_uses[t];
                 }
-                for (int it = 0; it < 2 * w.n_max && ok; ++it, ++kv_loads) {  // K_0, V_0, K_1, V_1, ...
+                // ring order = the order the MMA stream consumes the tiles: K_0 V_0 K_1 V_1 ..., or with double-
+                // buffered scores K_0 K_1 V_0 K_2 V_1 K_3 ... (S(j+2) follows P(j) V_j)
+                for (int it = 0; it < 2 * w.n_max && ok; ++it, ++kv_loads) {
+                    bool is_v;
+                    int tile;
+                    if (kDoubleS) {
+                        const int n = w.n_max;
+                        const int lead = n > 1 ? 2 : 1;
+                        if (it < lead) {
+                            is_v = false;
+                            tile = it;
+                        } else {
+                            const int f = it - lead, kk = n - lead;  // kk K tiles still to come, one after each V
+                            is_v = f >= 2 * kk || (f & 1) == 0;
+                            tile = f < 2 * kk ? (is_v ? (f >> 1) : (f >> 1) + 2) : kk + (f - 2 * kk);
+                        }
+                    } else {
+                        is_v = (it & 1) != 0;
+                        tile = it >> 1;
+                    }
                     const uint32_t slot = kv_loads % G::kSlots;
                     const uint32_t phase = (kv_loads / G::kSlots) & 1u;
                     ok = MbarWait(bar(kKvEmpty + slot), phase ^ 1u, abort_flag);
                     if (!ok) break;
                     MbarExpectTx(bar(kKvFull + slot), G::kKvTileBytes);
-                    const CUtensorMap* map = (it & 1) ? &map_v : &map_k;
+                    const CUtensorMap* map = is_v ? &map_v : &map_k;
                     for (int kb = 0; kb < G::kKBlocks; ++kb) {
                         TmaLoad4D(ring_smem + slot * G::kKvTileBytes + kb * G::kKvBlockBytes, map, bar(kKvFull + slot),
-                                  kb * 64, w.kv_tok0 + (it >> 1) * BN, w.h_kv, w.b);
+                                  kb * 64, w.kv_tok0 + tile * BN, w.h_kv, w.b);
                     }
                 }
             }
@@ -273,6 +299,7 @@ flash_fwd_sm100_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
             const uint64_t vmajor_hi = MakeSmemDesc(0, G::kKvBlockBytes, 1024);   // MN-major operand (V)
             const uint64_t q_desc[2] = {kmajor_hi | (q_smem >> 4), kmajor_hi | ((q_smem + G::kQTileBytes) >> 4)};
             const uint32_t s_tmem[2] = {tmem_base + G::kSCol, tmem_base + G::kSCol + 128};
+            uint32_t s_tmem_db = tmem_base + G::kSCol;  // current score buffer when the scores are double-buffered
             const uint32_t o_tmem[2] = {tmem_base + G::kOCol, tmem_base + G::kOCol + DP};
             auto issue_s = [&](int t, uint32_t slot) {
                 const uint64_t a0 = q_desc[t];
@@ -282,8 +309,9 @@ flash_fwd_sm100_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
                     constexpr int kStep = 32 >> 4;  // 16 elements = 32 bytes inside a 128-byte swizzle row
                     const uint32_t qa = ((ks >> 2) * G::kQBlockBytes >> 4) + (ks & 3) * kStep;
                     const uint32_t kb = ((ks >> 2) * G::kKvBlockBytes >> 4) + (ks & 3) * kStep;
-                    if (ks == 0) MmaSS<false>(s_tmem[t], a0 + qa, b0 + kb, idesc_s);
-                    else MmaSS<true>(s_tmem[t], a0 + qa, b0 + kb, idesc_s);
+                    const uint32_t d = kDoubleS ? s_tmem_db : s_tmem[t];
+                    if (ks == 0) MmaSS<false>(d, a0 + qa, b0 + kb, idesc_s);
+                    else MmaSS<true>(d, a0 + qa, b0 + kb, idesc_s);
                 }
             };
             auto issue_pv = [&](int t, uint32_t slot, bool first) {
@@ -291,15 +319,69 @@ flash_fwd_sm100_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
 #pragma unroll
                 for (int ks = 0; ks < BN / 16; ++ks) {
                     // 16 keys further: 8 packed P columns in tensor memory, 16 rows (2048 bytes) of V
-                    if (ks == 0) MmaTSFlag(o_tmem[t], s_tmem[t], b0, idesc_o, first ? 0u : 1u);
-                    else MmaTS<true>(o_tmem[t], s_tmem[t] + ks * 8, b0 + ks * (2048 >> 4), idesc_o);
+                    const uint32_t a = kDoubleS ? s_tmem_db : s_tmem[t];
+                    if (ks == 0) MmaTSFlag(o_tmem[t], a, b0, idesc_o, first ? 0u : 1u);
+                    else MmaTS<true>(o_tmem[t], a + ks * 8, b0 + ks * (2048 >> 4), idesc_o);
                 }
             };
             uint32_t q_uses[2] = {0, 0};    // items finished per query buffer
             uint32_t steps[2] = {0, 0};     // KV tiles processed per query tile (phase of s_full / p_full / o_done)
             uint32_t kv_base = 0;           // ring position of this item's K_0
             bool ok = true;
-            for (int r = 0; r < rounds && ok; ++r) {
+            if constexpr (kDoubleS) {
+                // single query tile, two score buffers: S(0), S(1), then P(j) V_j followed by S(j+2) into the buffer
+                // P(j) came from (same in-order stream, so the overwrite happens after the read)
+                uint32_t buf_uses[2] = {0, 0};  // P tiles consumed per score buffer (phase of p_full)
+                auto next_slot = [&](uint32_t* slot) {
+                    *slot = kv_base % G::kSlots;
+                    const uint32_t phase = (kv_base / G::kSlots) & 1u;
+                    ++kv_base;
+                    return MbarWait(bar(kKvFull + *slot), phase, abort_flag);
+                };
+                for (int r = 0; r < rounds && ok; ++r) {
+                    const int idx = item_of_round(r);
+                    if (idx < 0) continue;
+                    const Item w = decode_item(idx);
+                    const int n = w.n_max;
+                    if (n == 0) continue;
+                    ok = MbarWait(bar(kQFull), q_uses[0] & 1u, abort_flag);
+                    uint32_t slot = 0;
+                    for (int i = 0; i < 2 && i < n && ok; ++i) {
+                        ok = next_slot(&slot);
+                        if (!ok) break;
+                        TcFenceAfter();
+                        s_tmem_db = tmem_base + G::kSCol + i * 64;
+                        issue_s(0, slot);
+                        MmaCommit(bar(kSFull + i));
+                        if (i == n - 1) MmaCommit(bar(kQEmpty));
+                        MmaCommit(bar(kKvEmpty + slot));
+                    }
+                    for (int j = 0; j < n && ok; ++j) {
+                        const uint32_t buf = j & 1;
+                        ok = MbarWait(bar(kPFull + buf), buf_uses[buf] & 1u, abort_flag);
+                        ++buf_uses[buf];
+                        if (ok && j == 0 && q_uses[0] > 0) ok = MbarWait(bar(kOFree), (q_uses[0] - 1) & 1u, abort_flag);
+                        if (ok) ok = next_slot(&slot);  // V_j
+                        if (!ok) break;
+                        TcFenceAfter();
+                        s_tmem_db = tmem_base + G::kSCol + buf * 64;
+                        issue_pv(0, slot, j == 0);
+                        MmaCommit(bar(kODone + buf));
+                        MmaCommit(bar(kKvEmpty + slot));
+                        if (j + 2 < n) {
+                            ok = next_slot(&slot);  // K_j+2
+                            if (!ok) break;
+                            TcFenceAfter();
+                            issue_s(0, slot);
+                            MmaCommit(bar(kSFull + buf));
+                            if (j + 2 == n - 1) MmaCommit(bar(kQEmpty));
+                            MmaCommit(bar(kKvEmpty + slot));
+                        }
+                    }
+                    ++q_uses[0];
+                }
+            }
+            for (int r = 0; r < rounds && ok && !kDoubleS; ++r) {
                 const int idx = item_of_round(r);
                 if (idx < 0) continue;
                 const Item w = decode_item(idx);
@@ -360,9 +442,10 @@ flash_fwd_sm100_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
         const int quad = warp & 3;
         const int row_in_tile = quad * 32 + lane;
         const uint32_t lane_bits = static_cast<uint32_t>(quad * 32) << 16;
-        const uint32_t s_addr = tmem_base + lane_bits + G::kSCol + t * 128;
+        const uint32_t s_addr0 = tmem_base + lane_bits + G::kSCol + t * 128;
         const uint32_t o_addr = tmem_base + lane_bits + G::kOCol + t * DP;
         uint32_t steps = 0;  // KV tiles this group has processed (phase of s_full / p_full / o_done)
+        uint32_t buf_steps0 = 0, buf_steps1 = 0;  // double-buffered scores: tiles taken from each buffer
         bool ok = true;
 
         for (int r = 0; r < rounds && ok && t < QT; ++r) {
@@ -376,7 +459,18 @@ flash_fwd_sm100_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
             float l_sum = 0.0f;
 
             for (int j = 0; j < n_t; ++j, ++steps) {
-                ok = __all_sync(0xffffffffu, MbarWait(bar(kSFull + t), steps & 1u, abort_flag));
+                // which score buffer / barrier set this step uses, and the phases to wait for
+                const uint32_t buf = kDoubleS ? (j & 1) : 0;
+                const uint32_t s_addr = s_addr0 + buf * 64;
+                const int sync = kDoubleS ? static_cast<int>(buf) : t;          // index into s_full / p_full
+                const uint32_t s_phase = kDoubleS ? ((buf ? buf_steps1 : buf_steps0) & 1u) : (steps & 1u);
+                // the product P(j-1) V_j-1 that must be complete before O may be rescaled
+                const int prev_sync = kDoubleS ? static_cast<int>(buf ^ 1) : t;
+                const uint32_t prev_phase = kDoubleS ? (((buf ? buf_steps0 : buf_steps1) - 1) & 1u) : ((steps - 1) & 1u);
+                if (kDoubleS) {
+                    if (buf) ++buf_steps1; else ++buf_steps0;
+                }
+                ok = __all_sync(0xffffffffu, MbarWait(bar(kSFull + sync), s_phase, abort_flag));
                 if (!ok) break;
                 TcFenceAfter();
                 // One pass over the S row, 64 columns at a time. The exponentials use the reference point the row
@@ -417,7 +511,7 @@ flash_fwd_sm100_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
                     if (__any_sync(0xffffffffu, move)) {
                         const float alpha = move ? Exp2(m_ref - mx) : 1.0f;  // m_ref = -inf -> 0
                         if (j > 0) {
-                            ok = __all_sync(0xffffffffu, MbarWait(bar(kODone + t), (steps - 1) & 1u, abort_flag));
+                            ok = __all_sync(0xffffffffu, MbarWait(bar(kODone + prev_sync), prev_phase, abort_flag));
                             if (!ok) break;
                             TcFenceAfter();
     #pragma unroll 1
@@ -468,12 +562,17 @@ flash_fwd_sm100_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
                 l_sum += (part4[0] + part4[1]) + (part4[2] + part4[3]);
                 TmemWaitSt();
                 TcFenceBefore();
-                MbarArrive(bar(kPFull + t));
+                MbarArrive(bar(kPFull + sync));
             }
             if (!ok) break;
 
             // ---- epilogue: O / l -> global, optional LSE; O is handed back as soon as it is in registers ----
-            ok = __all_sync(0xffffffffu, MbarWait(bar(kODone + t), (steps - 1) & 1u, abort_flag));
+            if (kDoubleS) {
+                const uint32_t last = (n_t - 1) & 1;
+                ok = __all_sync(0xffffffffu, MbarWait(bar(kODone + last), ((last ? buf_steps1 : buf_steps0) - 1) & 1u, abort_flag));
+            } else {
+                ok = __all_sync(0xffffffffu, MbarWait(bar(kODone + t), (steps - 1) & 1u, abort_flag));
+            }
             if (!ok) break;
             TcFenceAfter();
             const float inv = l_sum > 0.0f ? 1.0f / l_sum : 0.0f;
