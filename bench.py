@@ -217,11 +217,13 @@ class PagedWorkload(Workload):
         self.k_new = torch.randn((self.NSEQ, HKV, D), generator=g, device=device, dtype=torch.bfloat16)
         self.v_new = torch.randn((self.NSEQ, HKV, D), generator=g, device=device, dtype=torch.bfloat16)
         self.mean_len = int(self.lens.mean()) + 1
+        # scheduling hint: longest sequences first (the host knows the lengths of its batch)
+        self.seq_order = torch.from_numpy(np.argsort(-self.lens, kind="stable").astype(np.int32)).to(device)
 
     def step(self):
         self.ops.kv_append_batched(self.k_pool, self.v_pool, self.k_new, self.v_new, self.page_table, self.seq_lens)
         self.out = self.ops.paged_attention(self.q, self.k_pool, self.v_pool, self.page_table, self.seq_lens,
-                                            block_size=self.BS, typical_len=self.mean_len)
+                                            block_size=self.BS, typical_len=self.mean_len, seq_order=self.seq_order)
 
     def work_per_step(self):
         toks = int((self.lens + 1).sum())

@@ -135,6 +135,10 @@ typedef struct ScaDecodeFwdParams {
     const int32_t* page_table; /* [batch, max_blocks_per_seq], -1 = unmapped (weight 0)           */
     int64_t block_size, max_blocks_per_seq, num_kv_blocks;
     const int32_t* seq_lens;   /* [batch] or NULL (= seq_kv for every sequence)                   */
+    /* Addition (no counterpart in the reference): optional scheduling hint, device int32 [batch], a permutation of
+     * 0 .. batch-1. Thread blocks are handed out in this order, so listing the longest sequences first shortens
+     * the tail of a ragged batch. NULL = sequence order. Results do not depend on it. */
+    const int32_t* seq_order;
 } ScaDecodeFwdParams;
 
 /* partial kernel + merge kernel on `stream` */

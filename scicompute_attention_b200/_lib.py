@@ -73,7 +73,7 @@ class DecodeFwdParams(C.Structure):
                 ("o_stride", DecodeStrides), ("scale", C.c_float), ("dtype", C.c_int32),
                 ("page_table", C.c_void_p), ("block_size", C.c_int64),
                 ("max_blocks_per_seq", C.c_int64), ("num_kv_blocks", C.c_int64),
-                ("seq_lens", C.c_void_p)]
+                ("seq_lens", C.c_void_p), ("seq_order", C.c_void_p)]
 
 
 class PagedDecodeParams(C.Structure):

@@ -281,7 +281,8 @@ int64_t DecodeSplitsFor(int64_t seq_kv, int64_t batch, int64_t kv_heads, int64_t
 }
 
 int64_t PagedSplitsFor(int64_t typical_len, int64_t num_seqs, int64_t kv_heads, int64_t group, int64_t sm_count) {
-    const int64_t by_balance = detail::Max<int64_t>(1, detail::Min<int64_t>(16, (typical_len + 512) / 1024));
+    // about 2048 tokens per split (measured on 256 ragged sequences: 2 splits at a mean of 4350 tokens beat 3 and 4)
+    const int64_t by_balance = detail::Max<int64_t>(1, detail::Min<int64_t>(16, (typical_len + 1024) / 2048));
     return detail::Max(by_balance, DecodeSplitsFor(typical_len, num_seqs, kv_heads, group, sm_count));
 }
 

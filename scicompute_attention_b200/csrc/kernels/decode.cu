@@ -77,7 +77,8 @@ decode_partial_kernel(const ScaDecodeFwdParams p, const int head_chunks) {
     const int hc = static_cast<int>(rest % head_chunks);
     rest /= head_chunks;
     const int hk = static_cast<int>(rest % p.num_kv_heads);
-    const int64_t b = rest / p.num_kv_heads;
+    const int64_t b_slot = rest / p.num_kv_heads;
+    const int64_t b = p.seq_order != nullptr ? static_cast<int64_t>(__ldg(p.seq_order + b_slot)) : b_slot;
     const int group = static_cast<int>(p.num_heads / p.num_kv_heads);
     const int head0 = hk * group + hc * 16;
     const int nheads = min(16, group - hc * 16);

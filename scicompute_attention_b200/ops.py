@@ -81,9 +81,9 @@ def splits_for(seq_kv: int, batch: int, num_kv_heads: int, group: int, sms: int)
 def paged_splits_for(typical_len: int, num_seqs: int, num_kv_heads: int, group: int, sms: int) -> int:
     """Split count for ragged paged batches: every sequence gets the same number of splits, each
     covering ceil(len / splits) of its tokens, so CTA work is proportional to the sequence length.
-    About 1024 tokens per split keeps the longest CTA short enough for the tail of the grid while
-    amortising the per-CTA prologue; never fewer splits than the contiguous rule asks for."""
-    by_balance = max(1, min(16, (typical_len + 512) // 1024))
+    About 2048 tokens per split keeps the longest CTA short enough for the tail of the grid while
+    amortising the per-CTA prologue and the merge; never fewer splits than the contiguous rule asks for."""
+    by_balance = max(1, min(16, (typical_len + 1024) // 2048))
     return max(by_balance, splits_for(typical_len, num_seqs, num_kv_heads, group, sms))
 
 
@@ -156,8 +156,11 @@ def decode_attention(q, k, v, *, scale=None, num_splits: int = 0, layout: str = 
 
 
 def paged_attention(q, k_pool, v_pool, page_table, seq_lens, *, block_size: int, scale=None,
-                    num_splits: int = 0, typical_len: int = 0, stream=None, return_stats: bool = False):
-    """Decode over page-table-indirected K/V (sca::paged_attention).
+                    num_splits: int = 0, typical_len: int = 0, stream=None, return_stats: bool = False,
+                    seq_order=None):
+    """Decode over page-table-indirected K/V (sca::paged_attention). seq_order (device int32 [num_seqs], a
+    permutation) is an optional scheduling hint: thread blocks are handed out in that order, longest first
+    shortens the tail of a ragged batch.
 
     q [num_seqs, H_q, 1, D]; pools [num_blocks, block_size, H_kv, D]; page_table int32
     [num_seqs, max_blocks_per_seq] on the device (-1 = unmapped); seq_lens int32 [num_seqs] on the
@@ -199,6 +202,10 @@ def paged_attention(q, k_pool, v_pool, page_table, seq_lens, *, block_size: int,
     p.scale = effective_scale(scale, d)
     p.dtype = dtype_id(q.dtype)
     p.seq_lens = seq_lens.data_ptr() if seq_lens is not None else None
+    if seq_order is not None:
+        if seq_order.dtype != torch.int32 or seq_order.numel() != s or not seq_order.is_cuda:
+            raise _lib.ScaError(4, "seq_order must be a device int32 permutation of the sequences")
+        p.seq_order = seq_order.data_ptr()
     pp = PagedDecodeParams()
     pp.base = p
     pp.page_table = page_table.data_ptr()

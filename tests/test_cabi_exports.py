@@ -31,7 +31,7 @@ def test_struct_sizes_match_header_layout():
     # exactly these sizes (a mismatch would shift every field after it)
     assert C.sizeof(_lib.DecodeStrides) == 24
     assert C.sizeof(_lib.KvCacheShape) == 32
-    assert C.sizeof(_lib.DecodeFwdParams) == 7 * 8 + 6 * 8 + 4 * 24 + 8 + 8 + 3 * 8 + 8
+    assert C.sizeof(_lib.DecodeFwdParams) == 7 * 8 + 6 * 8 + 4 * 24 + 8 + 8 + 3 * 8 + 8 + 8
     assert C.sizeof(_lib.FlashFwdParams) == 5 * 8 + 18 * 8 + 16 + 8 + 8
     assert C.sizeof(_lib.PagedDecodeParams) == C.sizeof(_lib.DecodeFwdParams) + 32
     assert C.sizeof(_lib.FlashVarlenParams) == 4 * 8 + 6 * 8 + 2 * 8 + 4 + 4 + 4 + 4 + 8 + 8

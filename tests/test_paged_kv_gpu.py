@@ -117,6 +117,13 @@ def run_paged(dt, lens, bs, hq, hkv, d, nblk, seed, splits=0, shuffle=True, unma
                                  lens_np if use_lens else None, bs)
     H.check_close(H.to_host_f32(out)[:, :, 0, :], expect, dt,
                   f"paged dt={dt} lens={list(lens)[:6]} bs={bs} Hq={hq} Hkv={hkv} D={d} splits={splits}")
+    if dt != ol.DT_F32 and nseq > 1:
+        # the scheduling hint (longest first) changes which thread block does what, never the result
+        order = torch.from_numpy(np.argsort(-lens_np, kind="stable").astype(np.int32)).cuda()
+        hinted = ops.paged_attention(H.to_device(qb, dt), lk, lv, torch.from_numpy(case["table"]).cuda(),
+                                     torch.from_numpy(lens_np).cuda() if use_lens else None, block_size=bs,
+                                     num_splits=splits, typical_len=int(np.mean(lens)), seq_order=order)
+        assert torch.equal(hinted, out)
 
 
 def test_block_sizes_at_257_tokens():
