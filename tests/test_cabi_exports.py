@@ -75,6 +75,19 @@ def test_python_ops_refuse_cpu_tensors():
     with pytest.raises(_lib.ScaError) as e:
         ops.decode_attention(q, k, k)
     assert "no CPU path" in str(e.value)
+    # every operator of the package answers the same way: there is no host fallback anywhere
+    packed = torch.zeros(8, 2, 64, dtype=torch.float16)
+    table = torch.zeros(1, 4, dtype=torch.int32)
+    for call in (lambda: ops.flash_attention(k, k, k),
+                 lambda: ops.flash_attention_varlen(packed, packed, packed, [0, 8], [0, 8]),
+                 lambda: ops.simt_attention(k, k, k),
+                 lambda: ops.decode_partials(q, k, k),
+                 lambda: ops.decode_triples(q, k, k),
+                 lambda: ops.paged_attention(q, torch.zeros(4, 2, 2, 64, dtype=torch.float16),
+                                             torch.zeros(4, 2, 2, 64, dtype=torch.float16), table, None, block_size=2)):
+        with pytest.raises(_lib.ScaError) as e:
+            call()
+        assert "no CPU path" in str(e.value)
 
 
 def test_new_entry_points_validate_before_touching_the_device():
