@@ -388,12 +388,14 @@ class LongContextWorkload(Workload):
         self.px = None
         if self.world > 1 and self.exchange == "peer":
             self.px = multi_gpu.PeerExchange(self.B * HQ, D, device)
+            # the whole step (partial kernel + exchange kernel) is one captured graph, replayed every step
+            self.graph, self.out = self.px.capture(self.q, self.k, self.v)
         else:
             self.launches_per_step = 3
 
     def step(self):
         if self.px is not None:
-            self.out = self.px.decode(self.q, self.k, self.v)
+            self.graph.replay()
         else:
             self.out = self.mg.sequence_split_decode(self.q, self.k, self.v)
 

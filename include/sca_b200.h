@@ -198,7 +198,9 @@ SCA_ABI int sca_launch_flash_varlen(const ScaFlashVarlenParams* params, void* st
  * buffers of all ranks over NVLink, a bounded wait until all ranks have done the same for `epoch`, and
  * the final merge into out [rows][D] (same rule as decode_splitk.cu:143-182, applied across ranks).
  * `epoch` starts at 1 and grows by 1 per call, identically on every rank; calls of one rank must be
- * ordered (one stream). peer_buffers[rank] is the rank's own buffer. If a peer does not show up within
+ * ordered (one stream). With epoch = 0 the kernel counts the calls itself in the buffer (every rank must then
+ * use 0 on every call): the parameters no longer change from step to step, so the step can be captured in a
+ * CUDA graph and replayed. peer_buffers[rank] is the rank's own buffer. If a peer does not show up within
  * about a second the kernel gives up, leaves `out` undefined and sets the status word that
  * sca_peer_exchange_status reads back (0 = all waits were satisfied). One process per GPU: ranks that
  * share a GPU would wait on kernels that cannot run at the same time. */

@@ -10,6 +10,7 @@
 //     [0, 256)    uint32 flags[64]    flags[s] = last epoch whose triples rank s has fully pushed here
 //     [256, 260)  uint32 arrived      CTAs of the running kernel that have finished pushing
 //     [260, 264)  int32  status       0, or 1 after a wait for a peer gave up
+//     [264, 268)  uint32 epoch        epochs completed, when the kernel keeps the count itself (params.epoch == 0)
 //     [512, ...)  float  data[2][world][rows][2 + D]     (two epochs in turn)
 // Per launch (epoch e, parity e & 1) a CTA
 //   1. merges the local splits of its rows and stores the triples into data[parity][rank] of EVERY rank;
@@ -33,6 +34,7 @@ constexpr int kHeaderBytes = 512;
 constexpr int kFlagsOffset = 0;      // uint32[64]
 constexpr int kArrivedOffset = 256;  // uint32
 constexpr int kStatusOffset = 260;   // int32
+constexpr int kEpochOffset = 264;    // uint32
 constexpr int kMaxRanks = SCA_PEER_MAX_RANKS;
 constexpr long long kPeerWaitCycles = 2000000000LL;  // about a second: far beyond any legitimate skew inside a step
 
@@ -62,9 +64,18 @@ seqsplit_exchange_kernel(const ExchangeParams p) {
     constexpr int kCols = 2;     // head-dim columns per thread: d = threadIdx.x + 128 c, head_dim <= 256
     const int width = 2 + p.head_dim;
     const size_t half_floats = static_cast<size_t>(p.world) * p.rows * width;
-    const size_t slot = (p.epoch & 1u) * half_floats;
     unsigned char* local = p.peer[p.rank];
     __shared__ int s_ok;
+    __shared__ unsigned s_epoch;
+    // The epoch is either given by the host or counted in the buffer header, which makes the launch parameters
+    // identical from step to step (a captured graph can then replay the step). Every CTA reads the count before it
+    // counts itself in `arrived`; the last CTA to arrive advances it, so no CTA can see the new value too early.
+    if (threadIdx.x == 0) {
+        s_epoch = p.epoch != 0 ? p.epoch : *reinterpret_cast<volatile unsigned*>(local + kEpochOffset) + 1u;
+    }
+    __syncthreads();
+    const unsigned epoch = s_epoch;
+    const size_t slot = (epoch & 1u) * half_floats;
 
     // 1. local splits -> one triple per row, stored into every rank's buffer
     for (int row = blockIdx.x; row < p.rows; row += gridDim.x) {
@@ -108,9 +119,10 @@ seqsplit_exchange_kernel(const ExchangeParams p) {
         const unsigned before = atomicAdd(arrived, 1u);
         if (before == gridDim.x - 1) {
             *arrived = 0;  // ready for the next launch (same stream)
+            *reinterpret_cast<unsigned*>(local + kEpochOffset) = epoch;
             __threadfence_system();
             for (int r = 0; r < p.world; ++r) {
-                StoreReleaseSys(reinterpret_cast<unsigned*>(p.peer[r] + kFlagsOffset) + p.rank, p.epoch);
+                StoreReleaseSys(reinterpret_cast<unsigned*>(p.peer[r] + kFlagsOffset) + p.rank, epoch);
             }
         }
         // 3. bounded wait for every rank's epoch
@@ -118,7 +130,7 @@ seqsplit_exchange_kernel(const ExchangeParams p) {
         int ok = 1;
         const long long start = clock64();
         for (int s = 0; s < p.world && ok; ++s) {
-            while (static_cast<int>(LoadAcquireSys(flags + s) - p.epoch) < 0) {
+            while (static_cast<int>(LoadAcquireSys(flags + s) - epoch) < 0) {
                 if (clock64() - start > kPeerWaitCycles) {
                     ok = 0;
                     *reinterpret_cast<int*>(local + kStatusOffset) = 1;

@@ -104,7 +104,6 @@ class PeerExchange:
         if self.world > _lib.PEER_MAX_RANKS:
             raise ValueError(f"at most {_lib.PEER_MAX_RANKS} ranks")
         self.rows, self.head_dim, self.device = rows, head_dim, torch.device(device)
-        self.epoch = 0
         l = _lib.lib()
         nbytes = l.sca_peer_buffer_bytes(self.world, rows, head_dim)
         if nbytes < 0:
@@ -149,17 +148,33 @@ class PeerExchange:
             ws[: self.rows] = float("-inf")
             pm, pl, po = ws[: self.rows], ws[self.rows: 2 * self.rows], ws[2 * self.rows:]
         out = torch.empty((self.rows, d), dtype=q.dtype, device=q.device)
-        self.epoch += 1
         x = _lib.SeqSplitExchange()
         for r, ptr in enumerate(self._peers):
             x.peer_buffers[r] = ptr
         x.rank, x.world = self.rank, self.world
         x.rows, x.head_dim, x.num_splits = self.rows, d, splits
-        x.epoch = self.epoch & 0xFFFFFFFF
+        x.epoch = 0  # the kernel counts the steps in the buffer: identical parameters every step (graph replay)
         x.partial_m, x.partial_l, x.partial_o = pm.data_ptr(), pl.data_ptr(), po.data_ptr()
         x.out, x.out_dtype = out.data_ptr(), ops.dtype_id(q.dtype)
         _lib.check(_lib.lib().sca_launch_seqsplit_exchange(C.byref(x), ops._stream_ptr(stream)))
         return out
+
+    def capture(self, q, k_shard, v_shard, *, scale=None, num_splits: int = 0):
+        """Captures one decode step over these (static) tensors - partial kernel + exchange kernel - in a CUDA
+        graph. Collective in effect: every rank must capture and later replay the same number of times.
+        Returns (graph, out); `graph.replay()` recomputes `out` from the current contents of q / k_shard / v_shard."""
+        import torch
+        side = torch.cuda.Stream(device=self.device)
+        side.wait_stream(torch.cuda.current_stream(self.device))
+        with torch.cuda.stream(side):
+            for _ in range(2):  # warm-up outside the capture: scratch pool, kernel attributes
+                self.decode(q, k_shard, v_shard, scale=scale, num_splits=num_splits, stream=side)
+            side.synchronize()
+            graph = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(graph, stream=side):
+                out = self.decode(q, k_shard, v_shard, scale=scale, num_splits=num_splits, stream=side)
+        torch.cuda.current_stream(self.device).wait_stream(side)
+        return graph, out
 
     def status(self) -> int:
         """0, or 1 if some launch gave up waiting for a peer (synchronises the device)."""

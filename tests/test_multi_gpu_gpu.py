@@ -61,6 +61,17 @@ def _worker(rank, world, port, result_dir):
     torch.cuda.synchronize()
     H.check_close(H.to_host_f32(out3).reshape(b, hq, 1, d), ol.attention_f64(qd, kd[:, :, :1], vd[:, :, :1], causal=True),
                   dt, f"peer exchange, one token, rank {rank}")
+    # the same step captured in a CUDA graph and replayed on new keys (the kernel counts the epochs itself)
+    kb4, kd4 = H.normal_inputs((b, hkv, skv, d), 30, dt)
+    k_static = H.to_device(np.ascontiguousarray(kb4[:, :, lo:hi]), dt, f"cuda:{rank}")
+    graph, out4 = px.capture(q, k_static, v)
+    for step in range(2):
+        kb5, kd5 = H.normal_inputs((b, hkv, skv, d), 31 + step, dt)
+        k_static.copy_(H.to_device(np.ascontiguousarray(kb5[:, :, lo:hi]), dt, f"cuda:{rank}"))
+        graph.replay()
+        torch.cuda.synchronize()
+        H.check_close(H.to_host_f32(out4).reshape(b, hq, 1, d), ol.attention_f64(qd, kd5, vd, causal=True), dt,
+                      f"peer exchange, graph replay {step}, rank {rank}")
     assert px.status() == 0
     px.close()
     with open(os.path.join(result_dir, f"ok{rank}"), "w") as f:

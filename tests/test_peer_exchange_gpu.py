@@ -65,6 +65,17 @@ def test_single_rank_exchange_equals_split_k_decode_and_a_missing_peer_times_out
         H.check_close(H.to_host_f32(out).reshape(b, hq, 1, d), expect, dt, f"single-rank exchange, epoch {epoch}")
     assert _status(own) == 0
 
+    # epoch = 0: the kernel counts the steps itself (identical launch parameters every step, as a graph replay needs)
+    counted = _make_buffer(1, rows, d)
+    for step in range(3):
+        pm, pl, po, splits = ops.decode_partials(q, k, v, num_splits=4)
+        out = torch.empty((rows, d), dtype=q.dtype, device=q.device)
+        _lib.check(_exchange([counted], 0, 1, rows, d, splits, 0, pm, pl, po, out))
+        torch.cuda.synchronize()
+        H.check_close(H.to_host_f32(out).reshape(b, hq, 1, d), expect, dt, f"single-rank exchange, counted step {step}")
+    assert _status(counted) == 0
+    _lib.check(_lib.lib().sca_peer_buffer_destroy(counted))
+
     # head dims 64 and 256 (two columns per thread at 256)
     for d2, seed in ((64, 80), (256, 90)):
         qb2, qd2 = H.normal_inputs((1, 8, 1, d2), seed, ol.DT_BF16)
