@@ -11,17 +11,6 @@
 namespace sca_b200 {
 namespace sm100 {
 
-// ---- register budget per warp role ------------------------------------------------------------------
-// All four warps of a warpgroup must execute these together; the counts must be multiples of 8.
-template <int kRegs>
-__device__ __forceinline__ void RegDealloc() {
-    asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(kRegs));
-}
-template <int kRegs>
-__device__ __forceinline__ void RegAlloc() {
-    asm volatile("setmaxnreg.inc.sync.aligned.u32 %0;" ::"n"(kRegs));
-}
-
 // ---- mbarrier ------------------------------------------------------------------------------------
 __device__ __forceinline__ void MbarInit(uint32_t bar, uint32_t count) {
     asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count) : "memory");
