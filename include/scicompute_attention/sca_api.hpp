@@ -495,6 +495,10 @@ public:
                                  sci::Stream* stream);
     // Device int32 [max_num_seqs] sequence lengths as of the last AppendTokenBatch / SyncPageTable.
     const int32_t* SeqLensDevicePtr() const noexcept;
+    // Addition: device int32 permutation of [0, num_seqs), longest sequence first as of the last table
+    // sync - a scheduling hint for paged_attention (thread blocks of long sequences start first). Null
+    // when the stored order does not reduce to a permutation of the first `num_seqs` slots.
+    const int32_t* SeqOrderDevicePtr(int64_t num_seqs) const noexcept;
 
 private:
     KVCacheConfig cfg_{};
@@ -514,6 +518,8 @@ private:
     // incremental sync state (additions): leading entries of each device row that may differ from -1
     std::vector<int64_t> live_on_device_;
     sci::Tensor seq_lens_device_;
+    sci::Tensor seq_order_device_;
+    int64_t seq_order_extent_{-1};  // slots at or beyond this index were empty when the order was built; -1 = none built
 };
 
 // ================================================================================================

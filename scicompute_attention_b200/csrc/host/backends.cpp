@@ -677,6 +677,7 @@ sci::Result<AttentionResult> RunPaged(const sci::Tensor& q, const PagedKVCache& 
     p.scale = EffectiveScale(cfg, shape);
     p.dtype = DtypeId(q.dtype());
     p.seq_lens = params.seq_lens;
+    p.seq_order = kv.SeqOrderDevicePtr(num_seqs);  // scheduling hint only: any permutation gives the same result
     pp.page_table = table;
     pp.block_size = block_size;
     pp.max_blocks_per_seq = max_blocks;

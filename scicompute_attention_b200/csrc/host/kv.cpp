@@ -5,6 +5,7 @@
 // through the C ABI (sca_launch_kv_*), and the page table is mirrored to the device row by row
 // instead of as one O(max_seqs * num_blocks) upload.
 #include <algorithm>
+#include <numeric>
 #include <string>
 
 #include "device/stream.hpp"
@@ -344,7 +345,9 @@ sci::Result<PagedKVCache> PagedKVCache::Create(const KVCacheConfig& cfg, sci::De
     cache.page_table_host_.assign(static_cast<size_t>(cfg.max_num_seqs * row_len), -1);
     cache.page_table_device_ = sci::Tensor(sci::TensorShape({cfg.max_num_seqs, row_len}), sci::DType::kInt32, device);
     cache.seq_lens_device_ = sci::Tensor(sci::TensorShape({cfg.max_num_seqs}), sci::DType::kInt32, device);
-    if (cache.page_table_device_.data() == nullptr || cache.seq_lens_device_.data() == nullptr) {
+    cache.seq_order_device_ = sci::Tensor(sci::TensorShape({cfg.max_num_seqs}), sci::DType::kInt32, device);
+    if (cache.page_table_device_.data() == nullptr || cache.seq_lens_device_.data() == nullptr ||
+        cache.seq_order_device_.data() == nullptr) {
         return sci::MakeUnexpected<PagedKVCache>(
             MakeStatus(AttnStatusCode::kKVCapacityExceeded, "PagedKVCache: page table allocation failed"));
     }
@@ -525,6 +528,10 @@ sci::Status PagedKVCache::ResetSeq(int64_t seq_id, sci::Stream* stream) {
 const int32_t* PagedKVCache::PageTableDevicePtr() const noexcept {
     return static_cast<const int32_t*>(page_table_device_.data());
 }
+const int32_t* PagedKVCache::SeqOrderDevicePtr(int64_t num_seqs) const noexcept {
+    if (seq_order_extent_ < 0 || num_seqs < seq_order_extent_ || num_seqs > cfg_.max_num_seqs) return nullptr;
+    return static_cast<const int32_t*>(seq_order_device_.data());
+}
 int64_t PagedKVCache::LogicalBlockCount(int64_t seq_id) const noexcept {
     return (seq_id < 0 || seq_id >= cfg_.max_num_seqs) ? 0 : static_cast<int64_t>(seq_blocks_[static_cast<size_t>(seq_id)].size());
 }
@@ -558,6 +565,18 @@ sci::Status PagedKVCache::ForceSyncPageTable(sci::Stream* stream) {
     }
     if (stream != nullptr) device.copy_async(seq_lens_device_.data(), lens.data(), lens.size() * sizeof(int32_t), *stream);
     else device.copy_to_device(seq_lens_device_.data(), lens.data(), lens.size() * sizeof(int32_t));
+    // launch order for the decode kernel: longest sequence first, ties and empty slots by index, so that the
+    // first n entries are a permutation of [0, n) whenever every slot from n on is empty
+    std::vector<int32_t> order(lens.size());
+    std::iota(order.begin(), order.end(), 0);
+    std::stable_sort(order.begin(), order.end(), [&lens](int32_t a, int32_t b) { return lens[static_cast<size_t>(a)] > lens[static_cast<size_t>(b)]; });
+    int64_t extent = 0;
+    for (int64_t s = 0; s < cfg_.max_num_seqs; ++s) {
+        if (lens[static_cast<size_t>(s)] > 0) extent = s + 1;
+    }
+    if (stream != nullptr) device.copy_async(seq_order_device_.data(), order.data(), order.size() * sizeof(int32_t), *stream);
+    else device.copy_to_device(seq_order_device_.data(), order.data(), order.size() * sizeof(int32_t));
+    seq_order_extent_ = extent;
     synced_revision_ = revision_;
     return sci::Status::Ok();
 }

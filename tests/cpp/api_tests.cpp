@@ -772,4 +772,59 @@ TEST(PagedKv, IsolationExhaustionResetAndAttention) {
     EXPECT_FALSE(sca::paged_attention(wrong, cache, params, {}).ok());
 }
 
+TEST(PagedKv, LaunchOrderIsLongestFirstAndOnlyOfferedWhenItIsAPermutation) {
+    auto dev = Gpu();
+    if (!dev) SKIP_TEST("no CUDA device");
+    sca::KVCacheConfig cfg;
+    cfg.num_layers = 1;
+    cfg.num_kv_heads = 1;
+    cfg.head_dim = 32;
+    cfg.block_size = 8;
+    cfg.num_blocks = 16;
+    cfg.max_num_seqs = 4;
+    auto created = sca::PagedKVCache::Create(cfg, *dev);
+    ASSERT_TRUE(created.ok());
+    sca::PagedKVCache cache = std::move(*created);
+    EXPECT_TRUE(cache.SeqOrderDevicePtr(4) == nullptr);  // nothing synced yet
+    auto tokens = [&](int64_t n) {
+        return ToDevice({n, 1, 32}, cfg.dtype, Encode(RandomFloats(size_t(n * 32), 21), cfg.dtype).bytes, *dev);
+    };
+    sci::Tensor t3 = tokens(3), t17 = tokens(17), t9 = tokens(9);
+    ASSERT_TRUE(cache.AppendTokens(0, 0, t3, t3, nullptr).ok());
+    ASSERT_TRUE(cache.AppendTokens(1, 0, t17, t17, nullptr).ok());
+    ASSERT_TRUE(cache.AppendTokens(2, 0, t9, t9, nullptr).ok());
+    ASSERT_TRUE(cache.SyncPageTable(nullptr).ok());
+    const int32_t* order_dev = cache.SeqOrderDevicePtr(4);
+    ASSERT_TRUE(order_dev != nullptr);
+    int32_t order[4] = {-1, -1, -1, -1};
+    dev->copy_to_host(order, order_dev, sizeof(order));
+    EXPECT_EQ(order[0], 1);
+    EXPECT_EQ(order[1], 2);
+    EXPECT_EQ(order[2], 0);
+    EXPECT_EQ(order[3], 3);
+    EXPECT_TRUE(cache.SeqOrderDevicePtr(3) == order_dev);  // slot 3 is empty: the first three entries permute [0, 3)
+    EXPECT_TRUE(cache.SeqOrderDevicePtr(2) == nullptr);   // slot 2 is live: no permutation of [0, 2) in there
+    EXPECT_TRUE(cache.SeqOrderDevicePtr(5) == nullptr);
+    // the order is a scheduling hint: attention over three sequences equals attention over each one alone
+    const std::vector<float> qvals = RandomFloats(3 * 2 * 32, 5);
+    sci::Tensor q = ToDevice({3, 2, 1, 32}, cfg.dtype, Encode(qvals, cfg.dtype).bytes, *dev);
+    sci::Tensor q0 = ToDevice({1, 2, 1, 32}, cfg.dtype,
+                              Encode(std::vector<float>(qvals.begin(), qvals.begin() + 2 * 32), cfg.dtype).bytes, *dev);
+    sca::PagedAttentionParams params;
+    params.seq_lens = cache.SeqLensDevicePtr();
+    params.num_seqs = 3;
+    const auto all = sca::paged_attention(q, cache, params, {});
+    ASSERT_TRUE(all.ok());
+    const std::vector<float> got = ReadFloats(all->out);
+    ASSERT_TRUE(cache.ResetSeq(1, nullptr).ok());
+    ASSERT_TRUE(cache.ResetSeq(2, nullptr).ok());
+    ASSERT_TRUE(cache.SyncPageTable(nullptr).ok());
+    params.num_seqs = 1;
+    const auto first = sca::paged_attention(q0, cache, params, {});  // q row 0 against sequence 0 alone
+    ASSERT_TRUE(first.ok());
+    const std::vector<float> alone = ReadFloats(first->out);
+    ASSERT_EQ(alone.size(), size_t(2 * 32));
+    for (size_t i = 0; i < alone.size(); ++i) EXPECT_TRUE(std::fabs(got[i] - alone[i]) <= 1e-3f);
+}
+
 int main(int argc, char** argv) { return mini::RunAll(argc, argv); }
