@@ -70,14 +70,22 @@ typedef struct ScaDeviceProbe {
     int cuda_available;
     int binary_has_sm80;   /* kept for source compatibility; always 1 (sm_100a is a superset)   */
     int binary_has_sm90;   /* kept for source compatibility; always 1                           */
-    /* additions for Blackwell (no counterpart in the reference) */
-    int binary_has_sm100a; /* this library carries sm_100a code (tcgen05 / TMEM / TMA)           */
-    int tmem_columns;      /* tensor-memory columns per SM (512 on sm_100), 0 when absent        */
-    int max_cluster_size;  /* portable thread-block-cluster limit                                */
-} ScaDeviceProbe;
+} ScaDeviceProbe;          /* same fields, order and size as the reference struct: a caller built
+                              against src/runtime/device_probe.h passes its own struct unchanged */
 
 /* Fills `out` for `device_id`. 0 on success, non-zero CUDA error code otherwise. */
 SCA_ABI int sca_probe_device(int device_id, ScaDeviceProbe* out);
+
+/* Blackwell additions (no counterpart in the reference): the reference probe followed by what the
+ * sm_100a kernels need to know. Kept in a struct of its own so that sca_probe_device never writes
+ * past the end of a reference-sized ScaDeviceProbe. */
+typedef struct ScaDeviceProbeB200 {
+    ScaDeviceProbe base;
+    int binary_has_sm100a; /* this library carries sm_100a code (tcgen05 / TMEM / TMA)           */
+    int tmem_columns;      /* tensor-memory columns per SM (512 on sm_100), 0 when absent        */
+    int max_cluster_size;  /* portable thread-block-cluster limit                                */
+} ScaDeviceProbeB200;
+SCA_ABI int sca_probe_device_b200(int device_id, ScaDeviceProbeB200* out);
 /* cudaMemGetInfo wrapper for the current device. 0 on success. */
 SCA_ABI int sca_mem_get_info(unsigned long long* free_bytes, unsigned long long* total_bytes);
 
@@ -135,11 +143,7 @@ typedef struct ScaDecodeFwdParams {
     const int32_t* page_table; /* [batch, max_blocks_per_seq], -1 = unmapped (weight 0)           */
     int64_t block_size, max_blocks_per_seq, num_kv_blocks;
     const int32_t* seq_lens;   /* [batch] or NULL (= seq_kv for every sequence)                   */
-    /* Addition (no counterpart in the reference): optional scheduling hint, device int32 [batch], a permutation of
-     * 0 .. batch-1. Thread blocks are handed out in this order, so listing the longest sequences first shortens
-     * the tail of a ragged batch. NULL = sequence order. Results do not depend on it. */
-    const int32_t* seq_order;
-} ScaDecodeFwdParams;
+} ScaDecodeFwdParams;          /* 248 bytes: field for field the reference's DecodeFwdParams      */
 
 /* partial kernel + merge kernel on `stream` */
 SCA_ABI int sca_launch_decode_splitk(const ScaDecodeFwdParams* params, void* stream);
@@ -155,6 +159,14 @@ typedef struct ScaPagedDecodeParams {
 } ScaPagedDecodeParams;
 
 SCA_ABI int sca_launch_paged_attention(const ScaPagedDecodeParams* params, void* stream);
+
+/* Paged attention with a scheduling hint (no counterpart in the reference). `seq_order` is a device
+ * int32 [batch] permutation of 0 .. batch-1; thread blocks are handed out in that order, so listing the
+ * longest sequences first shortens the tail of a ragged batch. Results do not depend on it; entries
+ * outside 0 .. batch-1 are ignored (their thread blocks do nothing). NULL = sequence order, i.e. exactly
+ * sca_launch_paged_attention. */
+SCA_ABI int sca_launch_paged_attention_ordered(const ScaPagedDecodeParams* params,
+                                               const int32_t* seq_order, void* stream);
 
 /* Sequence-split decode across GPUs (no counterpart in the reference, which is single-GPU).
  * sca_launch_decode_triples runs the partial kernel and merges this GPU's splits WITHOUT the

@@ -2,13 +2,13 @@
 # TEST INFRASTRUCTURE. Compiles the reference's own host sources (unmodified, where they lie in
 # the reference checkout, CPU-only stub mode) plus oracle/ref_shim.cpp into
 # oracle/_ref/libsca_ref.so. Nothing is copied from the reference; only the built library lands
-# in oracle/_ref/ (git-ignored). Usage: oracle/build_ref.sh [reference_root]
+# in oracle/_ref/ (git-ignored). Usage: oracle/build_ref.sh <reference_root>   (or SCA_REFERENCE_ROOT=<reference_root>)
 set -euo pipefail
 HERE="$(cd "$(dirname "${BASH_SOURCE[0]}")" && pwd)"
-REF="${1:-/root/reference}"
+REF="${1:-${SCA_REFERENCE_ROOT:-}}"
 OUT="$HERE/_ref"
-if [ ! -d "$REF/src" ]; then
-    echo "build_ref: reference checkout not found at $REF (skipped)"
+if [ -z "$REF" ] || [ ! -d "$REF/src" ]; then
+    echo "build_ref: no reference checkout given (argument or SCA_REFERENCE_ROOT); skipped"
     exit 0
 fi
 mkdir -p "$OUT"

@@ -17,9 +17,9 @@ STATUS_NAMES = {0: "OK", 4: "InvalidArgument", 5: "NotImplemented", 100: "CudaEr
 
 # every symbol include/sca_b200.h declares (tests check that the library exports all of them)
 EXPORTED_SYMBOLS = [
-    "sca_last_error", "sca_probe_device", "sca_mem_get_info", "sca_launch_flash_fwd",
+    "sca_last_error", "sca_probe_device", "sca_probe_device_b200", "sca_mem_get_info", "sca_launch_flash_fwd",
     "sca_flash_smem_bytes_for", "sca_launch_decode_splitk", "sca_launch_decode_splitk_paged",
-    "sca_launch_paged_attention", "sca_launch_decode_splitk_static", "sca_launch_decode_triples", "sca_launch_merge_triples",
+    "sca_launch_paged_attention", "sca_launch_paged_attention_ordered", "sca_launch_decode_splitk_static", "sca_launch_decode_triples", "sca_launch_merge_triples",
     "sca_launch_simt_forward", "sca_launch_kv_append", "sca_launch_kv_reset_block",
     "sca_launch_kv_gather", "sca_launch_kv_append_batched", "sca_launch_decode_partials",
     "sca_peer_buffer_bytes", "sca_peer_buffer_create", "sca_peer_buffer_open", "sca_peer_buffer_close",
@@ -46,8 +46,12 @@ class DeviceProbe(C.Structure):
                 ("smem_per_block_optin", C.c_ulonglong), ("regs_per_sm", C.c_ulonglong),
                 ("max_threads_per_sm", C.c_ulonglong), ("l2_bytes", C.c_ulonglong),
                 ("total_mem_bytes", C.c_ulonglong), ("free_mem_bytes", C.c_ulonglong),
-                ("cuda_available", C.c_int), ("binary_has_sm80", C.c_int), ("binary_has_sm90", C.c_int),
-                ("binary_has_sm100a", C.c_int), ("tmem_columns", C.c_int), ("max_cluster_size", C.c_int)]
+                ("cuda_available", C.c_int), ("binary_has_sm80", C.c_int), ("binary_has_sm90", C.c_int)]
+
+
+class DeviceProbeB200(C.Structure):
+    _fields_ = [("base", DeviceProbe), ("binary_has_sm100a", C.c_int), ("tmem_columns", C.c_int),
+                ("max_cluster_size", C.c_int)]
 
 
 class FlashFwdParams(C.Structure):
@@ -73,7 +77,7 @@ class DecodeFwdParams(C.Structure):
                 ("o_stride", DecodeStrides), ("scale", C.c_float), ("dtype", C.c_int32),
                 ("page_table", C.c_void_p), ("block_size", C.c_int64),
                 ("max_blocks_per_seq", C.c_int64), ("num_kv_blocks", C.c_int64),
-                ("seq_lens", C.c_void_p), ("seq_order", C.c_void_p)]
+                ("seq_lens", C.c_void_p)]
 
 
 class PagedDecodeParams(C.Structure):
@@ -116,6 +120,7 @@ def lib() -> C.CDLL:
     l = C.CDLL(KERNEL_LIB)
     l.sca_last_error.restype = C.c_char_p
     l.sca_probe_device.argtypes = [C.c_int, C.POINTER(DeviceProbe)]
+    l.sca_probe_device_b200.argtypes = [C.c_int, C.POINTER(DeviceProbeB200)]
     l.sca_mem_get_info.argtypes = [C.POINTER(C.c_ulonglong), C.POINTER(C.c_ulonglong)]
     if hasattr(l, "sca_launch_flash_fwd"):
         l.sca_launch_flash_fwd.argtypes = [C.POINTER(FlashFwdParams), C.c_void_p]
@@ -125,6 +130,7 @@ def lib() -> C.CDLL:
     l.sca_launch_decode_splitk.argtypes = [C.POINTER(DecodeFwdParams), C.c_void_p]
     l.sca_launch_decode_splitk_paged.argtypes = [C.POINTER(DecodeFwdParams), C.c_void_p]
     l.sca_launch_paged_attention.argtypes = [C.POINTER(PagedDecodeParams), C.c_void_p]
+    l.sca_launch_paged_attention_ordered.argtypes = [C.POINTER(PagedDecodeParams), C.c_void_p, C.c_void_p]
     l.sca_launch_decode_splitk_static.argtypes = [C.POINTER(DecodeFwdParams), C.c_void_p]
     l.sca_launch_decode_triples.argtypes = [C.POINTER(DecodeFwdParams), C.c_void_p, C.c_void_p]
     l.sca_launch_merge_triples.argtypes = [C.c_void_p, C.c_int64, C.c_int64, C.c_int64, C.c_void_p,

@@ -677,12 +677,13 @@ sci::Result<AttentionResult> RunPaged(const sci::Tensor& q, const PagedKVCache& 
     p.scale = EffectiveScale(cfg, shape);
     p.dtype = DtypeId(q.dtype());
     p.seq_lens = params.seq_lens;
-    p.seq_order = kv.SeqOrderDevicePtr(num_seqs);  // scheduling hint only: any permutation gives the same result
     pp.page_table = table;
     pp.block_size = block_size;
     pp.max_blocks_per_seq = max_blocks;
     pp.num_kv_blocks = kcfg.num_blocks;
-    if (sci::Status s = FromAbi(sca_launch_paged_attention(&pp, StreamHandle(cfg.stream))); !s.ok()) {
+    // scheduling hint only: any permutation gives the same result
+    const int32_t* order = kv.SeqOrderDevicePtr(num_seqs);
+    if (sci::Status s = FromAbi(sca_launch_paged_attention_ordered(&pp, order, StreamHandle(cfg.stream))); !s.ok()) {
         return sci::MakeUnexpected<AttentionResult>(s);
     }
     result.stats.used_backend = BackendKind::kPaged;

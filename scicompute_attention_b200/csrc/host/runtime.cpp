@@ -90,11 +90,12 @@ int g_cuda_available = -1;
 
 DeviceCapability ProbeDevice(int device_id) {
     DeviceCapability cap;
-    ScaDeviceProbe raw{};
-    if (sca_probe_device(device_id, &raw) != 0 || raw.cuda_available == 0) {
+    ScaDeviceProbeB200 ext{};
+    if (sca_probe_device_b200(device_id, &ext) != 0 || ext.base.cuda_available == 0) {
         cap.device_name = "cuda-unavailable";
         return cap;
     }
+    const ScaDeviceProbe& raw = ext.base;
     cap.device_name = raw.name;
     cap.major = raw.major;
     cap.minor = raw.minor;
@@ -113,9 +114,9 @@ DeviceCapability ProbeDevice(int device_id) {
     cap.has_tma_bulk = cc >= 90 && raw.binary_has_sm90 != 0;
     cap.has_wgmma = false;
     cap.has_fp8_mma = false;
-    cap.has_tcgen05 = cap.major == 10 && raw.binary_has_sm100a != 0;
-    cap.tmem_columns = raw.tmem_columns;
-    cap.max_cluster_size = raw.max_cluster_size;
+    cap.has_tcgen05 = cap.major == 10 && ext.binary_has_sm100a != 0;
+    cap.tmem_columns = ext.tmem_columns;
+    cap.max_cluster_size = ext.max_cluster_size;
     return cap;
 }
 

@@ -61,7 +61,7 @@ __device__ __forceinline__ int SwizzleV(int row, int chunk) {
 
 template <typename T, int D, bool kPaged, bool kHi>
 __global__ void __launch_bounds__(kThreads)
-decode_partial_kernel(const ScaDecodeFwdParams p, const int head_chunks) {
+decode_partial_kernel(const ScaDecodeFwdParams p, const int head_chunks, const int32_t* __restrict__ seq_order) {
     using G = DecodeGeom<D>;
     constexpr int CPR = G::kChunksPerRow;
     extern __shared__ __align__(128) unsigned char smem[];
@@ -78,13 +78,15 @@ decode_partial_kernel(const ScaDecodeFwdParams p, const int head_chunks) {
     rest /= head_chunks;
     const int hk = static_cast<int>(rest % p.num_kv_heads);
     const int64_t b_slot = rest / p.num_kv_heads;
-    const int64_t b = p.seq_order != nullptr ? static_cast<int64_t>(__ldg(p.seq_order + b_slot)) : b_slot;
+    const int64_t b = seq_order != nullptr ? static_cast<int64_t>(__ldg(seq_order + b_slot)) : b_slot;
+    if (static_cast<uint64_t>(b) >= static_cast<uint64_t>(p.batch)) return;  // a hint that is no permutation
     const int group = static_cast<int>(p.num_heads / p.num_kv_heads);
     const int head0 = hk * group + hc * 16;
     const int nheads = min(16, group - hc * 16);
 
     int64_t seq_len = p.seq_lens != nullptr ? static_cast<int64_t>(p.seq_lens[b]) : p.seq_kv;
     if (seq_len < 0) seq_len = 0;
+    if (!kPaged && seq_len > p.seq_kv) seq_len = p.seq_kv;  // never read past the K/V extent
     const int64_t chunk = (seq_len + p.num_splits - 1) / p.num_splits;
     const int64_t j_begin = static_cast<int64_t>(split) * chunk;
     const int64_t j_end = min(j_begin + chunk, seq_len);
@@ -396,7 +398,7 @@ decode_merge_kernel(const MergeSource src, const int64_t rows, const int parts, 
 }
 
 template <typename T, int D, bool kPaged, bool kHi>
-int LaunchPartial(const ScaDecodeFwdParams& p, int head_chunks, cudaStream_t stream) {
+int LaunchPartial(const ScaDecodeFwdParams& p, int head_chunks, const int32_t* seq_order, cudaStream_t stream) {
     using G = DecodeGeom<D>;
     const void* fn = reinterpret_cast<const void*>(&decode_partial_kernel<T, D, kPaged, kHi>);
     if (int rc = EnsureDynamicSmem(fn, G::kSmemBytes, "decode_partial_kernel")) return rc;
@@ -405,34 +407,34 @@ int LaunchPartial(const ScaDecodeFwdParams& p, int head_chunks, cudaStream_t str
         return Fail(SCA_INVALID_ARGUMENT, "decode: grid of " + std::to_string(blocks) + " blocks is out of range");
     }
     decode_partial_kernel<T, D, kPaged, kHi>
-        <<<static_cast<unsigned>(blocks), kThreads, G::kSmemBytes, stream>>>(p, head_chunks);
+        <<<static_cast<unsigned>(blocks), kThreads, G::kSmemBytes, stream>>>(p, head_chunks, seq_order);
     return CheckLaunch("decode_partial_kernel", stream);
 }
 
 template <typename T, int D>
-int LaunchPartialForDim(const ScaDecodeFwdParams& p, cudaStream_t stream) {
+int LaunchPartialForDim(const ScaDecodeFwdParams& p, const int32_t* seq_order, cudaStream_t stream) {
     const int group = static_cast<int>(p.num_heads / p.num_kv_heads);
     const int head_chunks = (group + 15) / 16;
     const bool paged = p.page_table != nullptr;
     const bool hi = group > 8;
     if (paged) {
-        return hi ? LaunchPartial<T, D, true, true>(p, head_chunks, stream)
-                  : LaunchPartial<T, D, true, false>(p, head_chunks, stream);
+        return hi ? LaunchPartial<T, D, true, true>(p, head_chunks, seq_order, stream)
+                  : LaunchPartial<T, D, true, false>(p, head_chunks, seq_order, stream);
     }
-    return hi ? LaunchPartial<T, D, false, true>(p, head_chunks, stream)
-              : LaunchPartial<T, D, false, false>(p, head_chunks, stream);
+    return hi ? LaunchPartial<T, D, false, true>(p, head_chunks, seq_order, stream)
+              : LaunchPartial<T, D, false, false>(p, head_chunks, seq_order, stream);
 }
 
 template <typename T>
-int LaunchPartialTyped(const ScaDecodeFwdParams& p, cudaStream_t stream) {
+int LaunchPartialTyped(const ScaDecodeFwdParams& p, const int32_t* seq_order, cudaStream_t stream) {
     switch (p.head_dim) {
-        case 32: return LaunchPartialForDim<T, 32>(p, stream);
-        case 64: return LaunchPartialForDim<T, 64>(p, stream);
-        case 96: return LaunchPartialForDim<T, 96>(p, stream);
-        case 128: return LaunchPartialForDim<T, 128>(p, stream);
-        case 160: return LaunchPartialForDim<T, 160>(p, stream);
-        case 192: return LaunchPartialForDim<T, 192>(p, stream);
-        case 256: return LaunchPartialForDim<T, 256>(p, stream);
+        case 32: return LaunchPartialForDim<T, 32>(p, seq_order, stream);
+        case 64: return LaunchPartialForDim<T, 64>(p, seq_order, stream);
+        case 96: return LaunchPartialForDim<T, 96>(p, seq_order, stream);
+        case 128: return LaunchPartialForDim<T, 128>(p, seq_order, stream);
+        case 160: return LaunchPartialForDim<T, 160>(p, seq_order, stream);
+        case 192: return LaunchPartialForDim<T, 192>(p, seq_order, stream);
+        case 256: return LaunchPartialForDim<T, 256>(p, seq_order, stream);
         default: break;
     }
     return Fail(SCA_INVALID_ARGUMENT,
@@ -504,10 +506,10 @@ int LaunchMergeOut(const ScaDecodeFwdParams& p, cudaStream_t stream) {
 // fp32 inputs take the SIMT partial kernel (simt.cu); declared here, defined there.
 int LaunchDecodePartialF32(const ScaDecodeFwdParams& p, cudaStream_t stream);
 
-int LaunchDecodePartials(const ScaDecodeFwdParams& p, cudaStream_t stream) {
+int LaunchDecodePartials(const ScaDecodeFwdParams& p, cudaStream_t stream, const int32_t* seq_order = nullptr) {
     switch (p.dtype) {
-        case SCA_DTYPE_F16: return LaunchPartialTyped<__half>(p, stream);
-        case SCA_DTYPE_BF16: return LaunchPartialTyped<__nv_bfloat16>(p, stream);
+        case SCA_DTYPE_F16: return LaunchPartialTyped<__half>(p, seq_order, stream);
+        case SCA_DTYPE_BF16: return LaunchPartialTyped<__nv_bfloat16>(p, seq_order, stream);
         case SCA_DTYPE_F32: return LaunchDecodePartialF32(p, stream);
         default: break;
     }
@@ -580,7 +582,8 @@ extern "C" int sca_launch_decode_splitk_paged(const ScaDecodeFwdParams* params, 
     return sca_launch_decode_splitk(params, stream);
 }
 
-extern "C" int sca_launch_paged_attention(const ScaPagedDecodeParams* params, void* stream) {
+extern "C" int sca_launch_paged_attention_ordered(const ScaPagedDecodeParams* params,
+                                                  const int32_t* seq_order, void* stream) {
     ClearError();
     if (params == nullptr || params->page_table == nullptr) {
         return Fail(SCA_INVALID_ARGUMENT, "paged attention: null page table");
@@ -590,7 +593,18 @@ extern "C" int sca_launch_paged_attention(const ScaPagedDecodeParams* params, vo
     p.block_size = params->block_size;
     p.max_blocks_per_seq = params->max_blocks_per_seq;
     p.num_kv_blocks = params->num_kv_blocks;
-    return sca_launch_decode_splitk_paged(&p, stream);
+    if (p.block_size <= 0 || p.max_blocks_per_seq <= 0 || p.num_kv_blocks <= 0) {
+        return Fail(SCA_INVALID_ARGUMENT,
+                    "paged attention: block_size/max_blocks_per_seq/num_kv_blocks must be positive");
+    }
+    if (int rc = ValidateDecode(&p, true)) return rc;
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    if (int rc = LaunchDecodePartials(p, s, seq_order)) return rc;
+    return LaunchMergeOut(p, s);
+}
+
+extern "C" int sca_launch_paged_attention(const ScaPagedDecodeParams* params, void* stream) {
+    return sca_launch_paged_attention_ordered(params, nullptr, stream);
 }
 
 // Partial kernel only: fills partial_m / partial_l / partial_o; the caller merges (sca_launch_seqsplit_exchange).

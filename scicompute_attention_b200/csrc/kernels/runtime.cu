@@ -96,7 +96,6 @@ extern "C" int sca_probe_device(int device_id, ScaDeviceProbe* out) {
     std::memset(out, 0, sizeof(*out));
     out->binary_has_sm80 = 1;
     out->binary_has_sm90 = 1;
-    out->binary_has_sm100a = 1;
     int count = 0;
     cudaError_t err = cudaGetDeviceCount(&count);
     if (err != cudaSuccess || count <= 0 || device_id < 0 || device_id >= count) {
@@ -127,8 +126,17 @@ extern "C" int sca_probe_device(int device_id, ScaDeviceProbe* out) {
         if (cudaMemGetInfo(&free_b, &total_b) == cudaSuccess) out->free_mem_bytes = free_b;
     }
     out->cuda_available = 1;
-    out->tmem_columns = (prop.major == 10) ? 512 : 0;
-    out->max_cluster_size = prop.major >= 9 ? 8 : 1;
+    return 0;
+}
+
+extern "C" int sca_probe_device_b200(int device_id, ScaDeviceProbeB200* out) {
+    if (out == nullptr) return 1;
+    std::memset(out, 0, sizeof(*out));
+    out->binary_has_sm100a = 1;
+    const int rc = sca_probe_device(device_id, &out->base);
+    if (rc != 0) return rc;
+    out->tmem_columns = (out->base.major == 10) ? 512 : 0;
+    out->max_cluster_size = out->base.major >= 9 ? 8 : 1;
     return 0;
 }
 

@@ -202,15 +202,16 @@ def paged_attention(q, k_pool, v_pool, page_table, seq_lens, *, block_size: int,
     p.scale = effective_scale(scale, d)
     p.dtype = dtype_id(q.dtype)
     p.seq_lens = seq_lens.data_ptr() if seq_lens is not None else None
+    order_ptr = None
     if seq_order is not None:
         if seq_order.dtype != torch.int32 or seq_order.numel() != s or not seq_order.is_cuda:
             raise _lib.ScaError(4, "seq_order must be a device int32 permutation of the sequences")
-        p.seq_order = seq_order.data_ptr()
+        order_ptr = seq_order.data_ptr()
     pp = PagedDecodeParams()
     pp.base = p
     pp.page_table = page_table.data_ptr()
     pp.block_size, pp.max_blocks_per_seq, pp.num_kv_blocks = bs, max_blocks, nblk
-    check(lib().sca_launch_paged_attention(C.byref(pp), _stream_ptr(stream)))
+    check(lib().sca_launch_paged_attention_ordered(C.byref(pp), order_ptr, _stream_ptr(stream)))
     if return_stats:
         return out, {"num_splits": splits, "workspace_bytes": base * (2 + d) * 4}
     return out

@@ -31,7 +31,10 @@ def test_struct_sizes_match_header_layout():
     # exactly these sizes (a mismatch would shift every field after it)
     assert C.sizeof(_lib.DecodeStrides) == 24
     assert C.sizeof(_lib.KvCacheShape) == 32
-    assert C.sizeof(_lib.DecodeFwdParams) == 7 * 8 + 6 * 8 + 4 * 24 + 8 + 8 + 3 * 8 + 8 + 8
+    # 248 = sizeof(DecodeFwdParams) of the reference (src/backends/decode/decode_splitk.cuh:23-51); the test that
+    # compiles the binding stubs against the reference's own headers asserts the same with static_assert
+    assert C.sizeof(_lib.DecodeFwdParams) == 7 * 8 + 6 * 8 + 4 * 24 + 8 + 8 + 3 * 8 + 8 == 248
+    assert C.sizeof(_lib.DeviceProbe) == 352 and C.sizeof(_lib.DeviceProbeB200) == 368
     assert C.sizeof(_lib.FlashFwdParams) == 5 * 8 + 18 * 8 + 16 + 8 + 8
     assert C.sizeof(_lib.PagedDecodeParams) == C.sizeof(_lib.DecodeFwdParams) + 32
     assert C.sizeof(_lib.FlashVarlenParams) == 4 * 8 + 6 * 8 + 2 * 8 + 4 + 4 + 4 + 4 + 8 + 8
@@ -61,10 +64,18 @@ def test_probe_without_a_device_reports_unavailable():
     import torch
     if torch.cuda.is_available():
         pytest.skip("a CUDA device is present")
-    probe = _lib.DeviceProbe()
-    rc = _lib.lib().sca_probe_device(0, C.byref(probe))
-    assert rc != 0 and probe.cuda_available == 0
+    probe = _lib.DeviceProbeB200()
+    rc = _lib.lib().sca_probe_device_b200(0, C.byref(probe))
+    assert rc != 0 and probe.base.cuda_available == 0
     assert probe.binary_has_sm100a == 1
+
+
+def test_reference_sized_probe_struct_is_not_overrun():
+    """sca_probe_device must write exactly the reference's struct (src/runtime/device_probe.h): a caller built against
+    that header hands in 352 bytes, so the bytes behind them must stay untouched."""
+    buf = (C.c_ubyte * (C.sizeof(_lib.DeviceProbe) + 64))(*([0xAB] * (C.sizeof(_lib.DeviceProbe) + 64)))
+    _lib.lib().sca_probe_device(0, C.cast(buf, C.POINTER(_lib.DeviceProbe)))
+    assert bytes(buf[C.sizeof(_lib.DeviceProbe):]) == bytes([0xAB] * 64)
 
 
 def test_python_ops_refuse_cpu_tensors():
