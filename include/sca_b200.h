@@ -113,6 +113,14 @@ typedef struct ScaFlashFwdParams {
 
 SCA_ABI int sca_launch_flash_fwd(const ScaFlashFwdParams* params, void* stream);
 
+/* Outcome of earlier flash launches on `device_id` (no counterpart in the reference, whose kernel has no waits
+ * that can give up). Every barrier wait inside the flash kernel is bounded; when one runs out the kernel stops,
+ * leaves its output undefined and stores 1 + the index of the warp that gave up in a per-device word. The launch
+ * call itself has long returned SCA_OK by then, so a caller that wants to know asks here after synchronising the
+ * stream: *status_out = 0 (every launch so far ran to completion) or that code; reading clears the word. With
+ * SCI_ATTENTION_DEBUG_SYNC=1 the launch call synchronises, checks the word itself and returns SCA_CUDA_ERROR. */
+SCA_ABI int sca_flash_status(int device_id, int32_t* status_out);
+
 /* Shared-memory bytes of one flash tile (replaces FlashSmemBytesFor, flash_fwd_kernel.cuh:56).
  * On sm_100a: Q tile + `stages` K tiles + `stages` V tiles, unpadded (TMA 128B swizzle needs no
  * row padding) + 1 KiB of barriers and alignment slack. Returns -1 for a non-positive argument. */
@@ -260,11 +268,17 @@ SCA_ABI int sca_launch_seqsplit_exchange(const ScaSeqSplitExchange* params, void
 SCA_ABI int sca_launch_decode_splitk_static(const ScaDecodeFwdParams* params, void* stream);
 
 /* ------------------------------------------------------------------------------------------ */
-/* reference-level backends kept for API completeness (functional, not tuned):                   */
-/* one SIMT kernel serves LaunchNaiveForward (src/backends/naive/attention_naive.cuh:60) and      */
-/* LaunchTiledForward (src/backends/tiled/attention_tiled.cuh:57) and the fp32 decode case.       */
-/* Same parameter block as the flash entry; dtype_id may also be SCA_DTYPE_F32.                   */
+/* reference-level backends kept for API completeness (functional, not tuned).                    */
+/* Parameter block of both: ScaFlashFwdParams; dtype_id may also be SCA_DTYPE_F32.               */
 /* ------------------------------------------------------------------------------------------ */
+/* Level-1 naive attention - replaces LaunchNaiveForward (src/backends/naive/attention_naive.cuh:28-60): scores,
+ * row softmax and P.V as three kernels with the score matrix MATERIALISED in `scores`, fp32
+ * [batch, heads, seq_q, seq_kv] = sca_naive_score_bytes(...) bytes of caller-provided device memory (the
+ * reference's NaiveFwdParams::scores). */
+SCA_ABI long long sca_naive_score_bytes(int64_t batch, int64_t heads, int64_t seq_q, int64_t seq_kv);
+SCA_ABI int sca_launch_naive_forward(const ScaFlashFwdParams* params, float* scores, void* stream);
+/* One SIMT kernel with a running softmax and no score matrix - replaces LaunchTiledForward
+ * (src/backends/tiled/attention_tiled.cuh:57); it is also the fp32 case of the decode partial kernel. */
 SCA_ABI int sca_launch_simt_forward(const ScaFlashFwdParams* params, void* stream);
 
 /* ------------------------------------------------------------------------------------------ */
@@ -280,7 +294,10 @@ typedef struct ScaKvCacheShape {
 SCA_ABI int sca_launch_kv_append(void* layer_k, void* layer_v, const void* k_new, const void* v_new,
                                  const int32_t* slot_mapping, int64_t num_tokens,
                                  const ScaKvCacheShape* shape, int64_t elem_bytes, void* stream);
-/* zeroes the listed blocks of K and V; ids < 0 or >= num_blocks are skipped */
+/* zeroes the listed blocks of K and V; ids < 0 or >= num_blocks are skipped. `block_ids` (here and in
+ * sca_launch_kv_gather) is normally device memory; a list in host memory is accepted too and copied to the
+ * device first, because the reference's PagedKVCache::ResetSeq passes the ids of a std::vector
+ * (src/kv_cache/paged_kv_cache.cpp:150-156). */
 SCA_ABI int sca_launch_kv_reset_block(void* layer_k, void* layer_v, const int32_t* block_ids,
                                       int64_t num_blocks, const ScaKvCacheShape* shape,
                                       int64_t elem_bytes, void* stream);

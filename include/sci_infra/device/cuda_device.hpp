@@ -33,6 +33,25 @@ private:
     std::string name_;
 };
 
+// While one of these is alive on a thread, CudaDevice::allocate / deallocate on that thread are ordered on
+// `cuda_stream` (cudaMallocAsync, the zero fill and cudaFreeAsync all go to that stream) instead of the legacy
+// default stream. The attention entry points open one for the stream of the call, so that a freshly allocated,
+// zero-filled output is ordered before the kernel that writes it on ANY kind of stream - a cudaStreamNonBlocking
+// stream does not synchronise with the legacy stream. When the scope closes on such a stream it leaves a marker
+// behind; memory that is released later, outside any scope, is freed only after that marker, i.e. after the last
+// work the library queued on a non-blocking stream of that device.
+class StreamOrderedScope {
+public:
+    explicit StreamOrderedScope(void* cuda_stream);
+    ~StreamOrderedScope();
+    StreamOrderedScope(const StreamOrderedScope&) = delete;
+    StreamOrderedScope& operator=(const StreamOrderedScope&) = delete;
+
+private:
+    void* previous_;
+    bool previous_active_;
+};
+
 class DeviceManager {
 public:
     static DeviceManager& Instance();

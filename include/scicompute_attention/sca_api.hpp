@@ -554,6 +554,12 @@ SCI_ATTENTION_API sci::Result<AttentionResult> flash_attention_varlen(const sci:
                                                                       const int32_t* cu_seqlens_kv, int64_t max_seq_q,
                                                                       int64_t max_seq_kv, const AttentionConfig& cfg);
 
+// Addition (no counterpart in the reference): whether every flash launch on `device_id` so far ran to completion.
+// All waits inside the flash kernel are bounded; a launch whose wait ran out leaves its output undefined, and this
+// call - made after synchronising the stream - is how a caller learns of it (kCudaError with the role that gave
+// up). Reading clears the record.
+SCI_ATTENTION_API sci::Status FlashLaunchStatus(int device_id = 0);
+
 struct DecodeConfig {
     int64_t num_splits{0};   // 0 -> automatic
     int64_t max_splits{64};  // cap of the automatic choice on B200 (the reference's laptop-GPU table stops at 16)

@@ -17,10 +17,10 @@ STATUS_NAMES = {0: "OK", 4: "InvalidArgument", 5: "NotImplemented", 100: "CudaEr
 
 # every symbol include/sca_b200.h declares (tests check that the library exports all of them)
 EXPORTED_SYMBOLS = [
-    "sca_last_error", "sca_probe_device", "sca_probe_device_b200", "sca_mem_get_info", "sca_launch_flash_fwd",
+    "sca_last_error", "sca_probe_device", "sca_probe_device_b200", "sca_mem_get_info", "sca_launch_flash_fwd", "sca_flash_status",
     "sca_flash_smem_bytes_for", "sca_launch_decode_splitk", "sca_launch_decode_splitk_paged",
     "sca_launch_paged_attention", "sca_launch_paged_attention_ordered", "sca_launch_decode_splitk_static", "sca_launch_decode_triples", "sca_launch_merge_triples",
-    "sca_launch_simt_forward", "sca_launch_kv_append", "sca_launch_kv_reset_block",
+    "sca_launch_simt_forward", "sca_naive_score_bytes", "sca_launch_naive_forward", "sca_launch_kv_append", "sca_launch_kv_reset_block",
     "sca_launch_kv_gather", "sca_launch_kv_append_batched", "sca_launch_decode_partials",
     "sca_peer_buffer_bytes", "sca_peer_buffer_create", "sca_peer_buffer_open", "sca_peer_buffer_close",
     "sca_peer_buffer_destroy", "sca_peer_exchange_status", "sca_launch_seqsplit_exchange",
@@ -124,9 +124,13 @@ def lib() -> C.CDLL:
     l.sca_mem_get_info.argtypes = [C.POINTER(C.c_ulonglong), C.POINTER(C.c_ulonglong)]
     if hasattr(l, "sca_launch_flash_fwd"):
         l.sca_launch_flash_fwd.argtypes = [C.POINTER(FlashFwdParams), C.c_void_p]
+        l.sca_flash_status.argtypes = [C.c_int, C.POINTER(C.c_int32)]
         l.sca_flash_smem_bytes_for.argtypes = [C.c_int, C.c_longlong, C.c_int, C.c_int, C.c_int]
         l.sca_flash_smem_bytes_for.restype = C.c_longlong
     l.sca_launch_simt_forward.argtypes = [C.POINTER(FlashFwdParams), C.c_void_p]
+    l.sca_launch_naive_forward.argtypes = [C.POINTER(FlashFwdParams), C.c_void_p, C.c_void_p]
+    l.sca_naive_score_bytes.argtypes = [C.c_int64] * 4
+    l.sca_naive_score_bytes.restype = C.c_longlong
     l.sca_launch_decode_splitk.argtypes = [C.POINTER(DecodeFwdParams), C.c_void_p]
     l.sca_launch_decode_splitk_paged.argtypes = [C.POINTER(DecodeFwdParams), C.c_void_p]
     l.sca_launch_paged_attention.argtypes = [C.POINTER(PagedDecodeParams), C.c_void_p]

@@ -121,9 +121,11 @@ def build_cpp_tests(force: bool = False, verbose: bool = False) -> str | None:
     deps = [src, os.path.join(ROOT, "tests", "cpp", "mini_test.hpp"), HOST_LIB, oracle_so] + _headers()
     if force or not _newer(exe, deps):
         cxx = shutil.which("g++") or "g++"
+        cuda = os.path.dirname(os.path.dirname(_nvcc()))
         _run([cxx, "-O1", "-std=c++20", "-Wall", "-I", INCLUDE, "-I", os.path.join(INCLUDE, "sci_infra"),
-              "-I", os.path.join(ROOT, "tests", "cpp"), src, "-o", exe, "-L", PKG, "-l:libsci_attention.so",
-              "-l:libsca_b200.so", "-L", os.path.join(ROOT, "oracle"), "-l:liboracle.so",
+              "-I", os.path.join(ROOT, "tests", "cpp"), "-I", os.path.join(cuda, "include"), src, "-o", exe,
+              "-L", PKG, "-l:libsci_attention.so", "-l:libsca_b200.so", "-L", os.path.join(ROOT, "oracle"),
+              "-l:liboracle.so", "-L", os.path.join(cuda, "lib64"), "-lcudart_static", "-lrt", "-ldl", "-lpthread",
               "-Wl,-rpath,$ORIGIN/../../scicompute_attention_b200", "-Wl,-rpath,$ORIGIN/../../oracle"])
     if verbose:
         print("built", exe)

@@ -6,6 +6,7 @@
 // tables:: (api.cpp) in place of the laptop-GPU ones.
 #include <string>
 
+#include "device/cuda_device.hpp"
 #include "internal.hpp"
 
 namespace sca {
@@ -89,9 +90,8 @@ size_t ScoreBytes(const AttentionShape& s) {
 }
 
 // =================================================================================================
-// naive: reference-level backend. On this build the score matrix is never materialised either (one
-// SIMT kernel with a running softmax), but the capability answer keeps the reference's accounting of
-// what a materialising implementation would need, and the workspace limit is still enforced.
+// naive: reference-level backend. As in the reference the fp32 score matrix is materialised in pooled scratch
+// (three plain kernels: scores, row softmax, P.V), reported in the stats, and bounded by the workspace limit.
 // =================================================================================================
 size_t NaiveWorkspaceLimit(const AttentionConfig& cfg) {
     if (cfg.workspace_limit_bytes != 0) return cfg.workspace_limit_bytes;
@@ -131,6 +131,7 @@ public:
 
     sci::Result<AttentionResult> Forward(const sci::Tensor& q, const sci::Tensor& k, const sci::Tensor& v,
                                          const AttentionConfig& cfg) const override {
+        const sci::StreamOrderedScope allocations_on_call_stream(StreamHandle(cfg.stream));
         const sci::Result<AttentionShape> inferred = InferShape(q, k, v, cfg.layout);
         if (!inferred.ok()) return sci::MakeUnexpected<AttentionResult>(inferred.error());
         const AttentionShape shape = *inferred;
@@ -150,15 +151,18 @@ public:
         if (sci::Status s = AllocateOutputs(q, shape, cfg.return_lse, &result); !s.ok()) {
             return sci::MakeUnexpected<AttentionResult>(s);
         }
+        const sci::Result<float*> scores =
+            runtime::AcquireScratchFp32(runtime::ScratchKind::kScoresFp32, need / sizeof(float), q.device());
+        if (!scores.ok()) return sci::MakeUnexpected<AttentionResult>(scores.error());
         const ScaFlashFwdParams p = PackForward(q, k, v, &result, cfg, shape);
-        if (sci::Status s = FromAbi(sca_launch_simt_forward(&p, StreamHandle(cfg.stream))); !s.ok()) {
+        if (sci::Status s = FromAbi(sca_launch_naive_forward(&p, *scores, StreamHandle(cfg.stream))); !s.ok()) {
             return sci::MakeUnexpected<AttentionResult>(s);
         }
         result.stats.used_backend = BackendKind::kNaive;
-        result.stats.workspace_bytes = 0;
-        result.stats.materialized_score_bytes = 0;
-        result.stats.note = std::string("reference path: one SIMT kernel with a running softmax, no score matrix in HBM; layout=") +
-                            LayoutName(cfg.layout);
+        result.stats.workspace_bytes = need;
+        result.stats.materialized_score_bytes = static_cast<int64_t>(need);
+        result.stats.note = std::string("reference path: FP32 score matrix materialized in HBM (") + std::to_string(need) +
+                            " B); layout=" + LayoutName(cfg.layout);
         if (cfg.causal) result.stats.note += ", causal(alignment=bottom-right)";
         return sci::Ok(std::move(result));
     }
@@ -206,13 +210,14 @@ public:
             r.tile = TiledGeometry();
         }
         r.supported = no.empty();
-        r.reason = r.supported ? "tiled tile=" + r.tile.ToString() + " keeps S in smem (workspace 0 B)" : no;
+        r.reason = r.supported ? "tiled tile=" + r.tile.ToString() + " keeps S in registers (workspace 0 B)" : no;
         return r;
     }
     size_t WorkspaceBytes(const AttentionConfig&, const AttentionShape&) const override { return 0; }
 
     sci::Result<AttentionResult> Forward(const sci::Tensor& q, const sci::Tensor& k, const sci::Tensor& v,
                                          const AttentionConfig& cfg) const override {
+        const sci::StreamOrderedScope allocations_on_call_stream(StreamHandle(cfg.stream));
         const sci::Result<AttentionShape> inferred = InferShape(q, k, v, cfg.layout);
         if (!inferred.ok()) return sci::MakeUnexpected<AttentionResult>(inferred.error());
         const AttentionShape shape = *inferred;
@@ -327,6 +332,7 @@ public:
 
     sci::Result<AttentionResult> Forward(const sci::Tensor& q, const sci::Tensor& k, const sci::Tensor& v,
                                          const AttentionConfig& cfg) const override {
+        const sci::StreamOrderedScope allocations_on_call_stream(StreamHandle(cfg.stream));
         const sci::Result<AttentionShape> inferred = InferShape(q, k, v, cfg.layout);
         if (!inferred.ok()) return sci::MakeUnexpected<AttentionResult>(inferred.error());
         const AttentionShape shape = *inferred;
@@ -359,6 +365,7 @@ public:
                                                int64_t num_seqs, const int32_t* cu_q, const int32_t* cu_kv,
                                                int64_t max_seq_q, int64_t max_seq_kv,
                                                const AttentionConfig& cfg) const override {
+        const sci::StreamOrderedScope allocations_on_call_stream(StreamHandle(cfg.stream));
         if (cu_q == nullptr || cu_kv == nullptr) {
             return Refuse(AttnStatusCode::kShapeMismatch, "varlen requires host-resident cu_seqlens_q/kv");
         }
@@ -506,6 +513,7 @@ public:
 
     sci::Result<AttentionResult> Forward(const sci::Tensor& q, const sci::Tensor& k, const sci::Tensor& v,
                                          const AttentionConfig& cfg) const override {
+        const sci::StreamOrderedScope allocations_on_call_stream(StreamHandle(cfg.stream));
         const sci::Result<AttentionShape> inferred = InferShape(q, k, v, cfg.layout);
         if (!inferred.ok()) return sci::MakeUnexpected<AttentionResult>(inferred.error());
         const AttentionShape shape = *inferred;
@@ -580,6 +588,7 @@ public:
 // =================================================================================================
 sci::Result<AttentionResult> RunPaged(const sci::Tensor& q, const PagedKVCache& kv, const PagedAttentionParams& params,
                                       const AttentionConfig& cfg) {
+    const sci::StreamOrderedScope allocations_on_call_stream(StreamHandle(cfg.stream));
     if (q.ndims() != 4) {
         return Refuse(AttnStatusCode::kShapeMismatch,
                       "paged_attention expects q=[num_seqs, H_q, seq_q, D]; got ndims=" + std::to_string(q.ndims()));
@@ -756,6 +765,13 @@ sci::Result<AttentionResult> flash_attention(const sci::Tensor& q, const sci::Te
                                              const AttentionConfig& cfg) {
     return kFlash.Forward(q, k, v, cfg);
 }
+sci::Status FlashLaunchStatus(int device_id) {
+    int32_t code = 0;
+    if (sci::Status s = FromAbi(sca_flash_status(device_id, &code)); !s.ok()) return s;
+    if (code == 0) return sci::Status::Ok();
+    return sci::Status(sci::StatusCode::kCudaError, "flash attention: an earlier launch gave up waiting on a barrier (role " +
+                                                         std::to_string(code) + "); its output is invalid");
+}
 sci::Result<AttentionResult> flash_attention_varlen(const sci::Tensor& q, const sci::Tensor& k, const sci::Tensor& v,
                                                     int64_t num_seqs, const int32_t* cu_q, const int32_t* cu_kv,
                                                     int64_t max_seq_q, int64_t max_seq_kv, const AttentionConfig& cfg) {
@@ -790,6 +806,11 @@ sci::Result<AttentionResult> paged_attention(const sci::Tensor& q, const PagedKV
     params.block_size = kv.BlockSize();
     params.max_blocks_per_seq = kv.MaxBlocksPerSeq();
     params.layer = 0;
+    // The cache keeps a device copy of its sequence lengths (current after SyncPageTable / AppendTokenBatch, which this
+    // form needs anyway for the table). The reference passes no lengths here and scans every mapped slot, so the
+    // zero-filled tail of a sequence's last block takes softmax weight; with the lengths the result is the attention
+    // over exactly the stored tokens. Identical whenever every length is a multiple of block_size.
+    params.seq_lens = kv.SeqLensDevicePtr();
     return RunPaged(q, kv, params, cfg);
 }
 

@@ -8,6 +8,7 @@
 #include <numeric>
 #include <string>
 
+#include "device/cuda_device.hpp"
 #include "device/stream.hpp"
 #include "internal.hpp"
 
@@ -275,6 +276,7 @@ sci::Result<sci::Tensor> KVCache::GatherV(int64_t layer, const int32_t* ids, int
 
 sci::Result<sci::Tensor> KVCache::GatherInternal(int64_t layer, const int32_t* block_ids, int64_t num_blocks, bool is_key,
                                                  sci::Stream* stream) const {
+    const sci::StreamOrderedScope allocations_on_call_stream(StreamHandle(stream));
     if (layer < 0 || layer >= cfg_.num_layers) {
         return sci::MakeUnexpected<sci::Tensor>(
             MakeStatus(AttnStatusCode::kShapeMismatch, "KVCache::Gather layer=" + std::to_string(layer) + " out of range"));
@@ -361,6 +363,7 @@ sci::Result<PagedKVCache> PagedKVCache::Create(const KVCacheConfig& cfg, sci::De
 
 sci::Status PagedKVCache::AppendTokens(int64_t seq_id, int64_t layer, const sci::Tensor& k_new, const sci::Tensor& v_new,
                                        sci::Stream* stream) {
+    const sci::StreamOrderedScope allocations_on_call_stream(StreamHandle(stream));
     if (seq_id < 0 || seq_id >= cfg_.max_num_seqs) {
         return MakeStatus(AttnStatusCode::kShapeMismatch, "PagedKVCache::AppendTokens seq_id=" + std::to_string(seq_id) +
                                                               " out of range [0," + std::to_string(cfg_.max_num_seqs) + ")");
@@ -421,6 +424,7 @@ sci::Status PagedKVCache::AppendTokens(int64_t seq_id, int64_t layer, const sci:
 
 sci::Status PagedKVCache::AppendTokenBatch(int64_t num_seqs, int64_t layer, const sci::Tensor& k_new, const sci::Tensor& v_new,
                                            sci::Stream* stream) {
+    const sci::StreamOrderedScope allocations_on_call_stream(StreamHandle(stream));
     if (num_seqs <= 0 || num_seqs > cfg_.max_num_seqs) {
         return MakeStatus(AttnStatusCode::kShapeMismatch, "PagedKVCache::AppendTokenBatch num_seqs=" + std::to_string(num_seqs) +
                                                               " out of range [1," + std::to_string(cfg_.max_num_seqs) + "]");
@@ -485,7 +489,13 @@ sci::Status PagedKVCache::AppendTokenBatch(int64_t num_seqs, int64_t layer, cons
         const_cast<void*>(storage_.K(layer).data()), const_cast<void*>(storage_.V(layer).data()), k_new.data(), v_new.data(),
         table_dev, static_cast<const int32_t*>(seq_lens_device_.data()), num_seqs, max_blocks_per_seq_, &shape,
         DtypeSize(cfg_.dtype), current.handle()));
-    if (!launched.ok()) return launched;
+    if (!launched.ok()) {
+        // nothing was stored: take the token back. Blocks attached above stay with their sequences (as after a failed
+        // AppendTokens, ResetSeq recovers them); the device lengths are now ahead of the host, so force the next sync.
+        for (int64_t s = 0; s < num_seqs; ++s) --seq_lengths_[static_cast<size_t>(s)];
+        ++revision_;
+        return launched;
+    }
     ++revision_;
     synced_revision_ = revision_;  // table and lengths on the device already reflect this step
     num_appends_ += num_seqs;

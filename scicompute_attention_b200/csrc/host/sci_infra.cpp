@@ -56,7 +56,15 @@ void WithDevice(int device, Fn&& fn) {
 
 }  // namespace
 
+// One CudaDevice object per GPU for the life of the process: library-internal tensors that outlive a call (the
+// scratch pool) keep a plain Device pointer, and callers are free to drop their handle at any time - the
+// reference's own tests create a fresh handle per case (tests/kernel/test_naive_correctness.cu:24-27).
 SCI_EXPORT std::shared_ptr<CudaDevice> CudaDevice::Create(int device_id) {
+    static std::mutex mu;
+    static auto* devices = new std::map<int, std::shared_ptr<CudaDevice>>();  // never destroyed
+    std::lock_guard<std::mutex> lock(mu);
+    auto it = devices->find(device_id);
+    if (it != devices->end()) return it->second;
     int count = 0;
     if (cudaGetDeviceCount(&count) != cudaSuccess || device_id < 0 || device_id >= count) {
         cudaGetLastError();
@@ -67,13 +75,15 @@ SCI_EXPORT std::shared_ptr<CudaDevice> CudaDevice::Create(int device_id) {
         cudaGetLastError();
         return nullptr;
     }
-    return std::shared_ptr<CudaDevice>(new CudaDevice(device_id, prop.name));
+    std::shared_ptr<CudaDevice> created(new CudaDevice(device_id, prop.name));
+    (*devices)[device_id] = created;
+    return created;
 }
 
-// Tensors come from the device's stream-ordered memory pool (cudaMallocAsync on the legacy default stream)
-// with the pool told to keep what is freed: a call that returns a newly allocated output every time, as the
-// attention entry points do, then costs neither a cudaMalloc nor the device-wide synchronisation of a
-// cudaFree. Frees are ordered on the legacy stream, i.e. after earlier work of every blocking stream.
+// Tensors come from the device's stream-ordered memory pool (cudaMallocAsync) with the pool told to keep what
+// is freed: a call that returns a newly allocated output every time, as the attention entry points do, then
+// costs neither a cudaMalloc nor the device-wide synchronisation of a cudaFree. Outside a StreamOrderedScope
+// allocation and release are ordered on the legacy default stream, inside one on the scope's stream.
 // Memory the pool holds counts as used in cudaMemGetInfo until cudaDeviceReset or process exit.
 namespace {
 bool PoolReady(int id) {
@@ -96,27 +106,110 @@ bool PoolReady(int id) {
 }
 }  // namespace
 
+// ---- stream-ordered scope (see cuda_device.hpp) -------------------------------------------------------
+namespace {
+thread_local void* g_scope_stream = nullptr;
+thread_local bool g_scope_active = false;
+
+struct LastWork {
+    cudaEvent_t event = nullptr;
+    bool recorded = false;
+};
+std::mutex& LastWorkMutex() {
+    static std::mutex mu;
+    return mu;
+}
+// Per device: marker after the last library work queued on a non-blocking stream. Leaked on purpose (events must
+// not be destroyed from a static destructor, after the CUDA runtime is gone).
+std::map<int, LastWork>& LastWorkMap() {
+    static auto* map = new std::map<int, LastWork>();
+    return *map;
+}
+
+bool IsNonBlocking(cudaStream_t stream) {
+    if (stream == nullptr || stream == cudaStreamLegacy || stream == cudaStreamPerThread) return false;
+    unsigned int flags = 0;
+    if (cudaStreamGetFlags(stream, &flags) != cudaSuccess) {
+        cudaGetLastError();
+        return false;
+    }
+    return (flags & cudaStreamNonBlocking) != 0;
+}
+bool IsCapturing(cudaStream_t stream) {
+    cudaStreamCaptureStatus status = cudaStreamCaptureStatusNone;
+    if (cudaStreamIsCapturing(stream, &status) != cudaSuccess) {
+        cudaGetLastError();
+        return false;
+    }
+    return status != cudaStreamCaptureStatusNone;
+}
+}  // namespace
+
+SCI_EXPORT StreamOrderedScope::StreamOrderedScope(void* cuda_stream)
+    : previous_(g_scope_stream), previous_active_(g_scope_active) {
+    g_scope_stream = cuda_stream;
+    g_scope_active = true;
+}
+
+SCI_EXPORT StreamOrderedScope::~StreamOrderedScope() {
+    cudaStream_t stream = static_cast<cudaStream_t>(g_scope_stream);
+    g_scope_stream = previous_;
+    g_scope_active = previous_active_;
+    if (!IsNonBlocking(stream) || IsCapturing(stream)) return;
+    int device = 0;
+    if (cudaGetDevice(&device) != cudaSuccess) {
+        cudaGetLastError();
+        return;
+    }
+    std::lock_guard<std::mutex> lock(LastWorkMutex());
+    LastWork& last = LastWorkMap()[device];
+    if (last.event == nullptr && cudaEventCreateWithFlags(&last.event, cudaEventDisableTiming) != cudaSuccess) {
+        cudaGetLastError();
+        last.event = nullptr;
+        return;
+    }
+    if (cudaEventRecord(last.event, stream) == cudaSuccess) last.recorded = true;
+    else cudaGetLastError();
+}
+
 SCI_EXPORT void* CudaDevice::allocate(size_t bytes) {
     void* ptr = nullptr;
     const size_t n = bytes == 0 ? 1 : bytes;
     WithDevice(id_, [&] {
         const bool pooled = PoolReady(id_);
-        const cudaError_t got = pooled ? cudaMallocAsync(&ptr, n, cudaStreamLegacy) : cudaMalloc(&ptr, n);
+        cudaStream_t stream = g_scope_active ? static_cast<cudaStream_t>(g_scope_stream) : cudaStreamLegacy;
+        const cudaError_t got = pooled ? cudaMallocAsync(&ptr, n, stream) : cudaMalloc(&ptr, n);
         if (got != cudaSuccess) {
             cudaGetLastError();
             ptr = nullptr;
             return;
         }
         // fresh tensors read as zero, like the host device's calloc
-        if (cudaMemsetAsync(ptr, 0, n, cudaStreamLegacy) != cudaSuccess) cudaGetLastError();
+        if (cudaMemsetAsync(ptr, 0, n, stream) != cudaSuccess) cudaGetLastError();
     });
     return ptr;
 }
 SCI_EXPORT void CudaDevice::deallocate(void* ptr) {
     if (ptr == nullptr) return;
     WithDevice(id_, [&] {
-        const cudaError_t freed = PoolReady(id_) ? cudaFreeAsync(ptr, cudaStreamLegacy) : cudaFree(ptr);
-        if (freed != cudaSuccess) cudaGetLastError();
+        if (!PoolReady(id_)) {
+            if (cudaFree(ptr) != cudaSuccess) cudaGetLastError();  // synchronises the device: nothing can be in flight
+            return;
+        }
+        cudaStream_t stream = cudaStreamLegacy;
+        if (g_scope_active) {
+            stream = static_cast<cudaStream_t>(g_scope_stream);  // a temporary of the running call: same stream
+        } else {
+            // released by the caller at some later time: after earlier work of every blocking stream (legacy-stream
+            // semantics) and after the last library work on a non-blocking stream of this device
+            std::lock_guard<std::mutex> lock(LastWorkMutex());
+            auto it = LastWorkMap().find(id_);
+            if (it != LastWorkMap().end() && it->second.recorded &&
+                cudaStreamWaitEvent(cudaStreamLegacy, it->second.event, 0) != cudaSuccess) {
+                cudaGetLastError();
+            }
+        }
+        if (cudaFreeAsync(ptr, stream) != cudaSuccess) cudaGetLastError();
     });
 }
 SCI_EXPORT void CudaDevice::copy_to_device(void* dst, const void* src, size_t bytes) {
@@ -172,14 +265,7 @@ SCI_EXPORT DeviceManager& DeviceManager::Instance() {
 
 SCI_EXPORT std::shared_ptr<Device> DeviceManager::get_device(DeviceType type, int index) {
     if (type != DeviceType::kCUDA) return std::shared_ptr<Device>(&HostDevice(), [](Device*) {});
-    static std::mutex mu;
-    static std::map<int, std::shared_ptr<CudaDevice>>* devices = new std::map<int, std::shared_ptr<CudaDevice>>();
-    std::lock_guard<std::mutex> lock(mu);
-    auto it = devices->find(index);
-    if (it != devices->end()) return it->second;
-    std::shared_ptr<CudaDevice> created = CudaDevice::Create(index);
-    if (created) (*devices)[index] = created;
-    return created;
+    return CudaDevice::Create(index);  // the per-GPU object is shared and immortal
 }
 
 // ---- stream ------------------------------------------------------------------------------------------

@@ -23,6 +23,8 @@ int FailCuda(cudaError_t err, const char* what);
 // cudaGetLastError() right after a launch (reference behaviour: src/runtime/launcher.cu:94-100);
 // honours SCI_ATTENTION_DEBUG_SYNC=1 by synchronising the stream and reporting the async error.
 int CheckLaunch(const char* kernel_name, cudaStream_t stream);
+// True when SCI_ATTENTION_DEBUG_SYNC=1 (CheckLaunch then synchronises the stream after every launch).
+bool DebugSyncEnabled();
 // Opt-in to > 48 KiB of dynamic shared memory once per kernel symbol.
 int EnsureDynamicSmem(const void* kernel, size_t bytes, const char* kernel_name);
 // Cached SM count of the current device.

@@ -691,19 +691,22 @@ int MakeMap(CUtensorMap* map, const void* base, int dtype_id, int64_t d, int64_t
     return SCA_OK;
 }
 
-// One host-visible word per process that kernels set when a bounded wait expires.
-int* ErrorWordDevicePtr(int** host_view) {
+// One host-visible word per device that a kernel sets when one of its bounded waits expires (1 + the warp that
+// gave up). The words live in one pinned, mapped, portable allocation; sca_flash_status reads and clears them.
+constexpr int kMaxStatusDevices = 64;
+
+int* ErrorWords(int** host_view) {
     static int* host = nullptr;
     static int* dev = nullptr;
     static std::once_flag once;
     std::call_once(once, [] {
-        if (cudaHostAlloc(reinterpret_cast<void**>(&host), sizeof(int), cudaHostAllocMapped | cudaHostAllocPortable) !=
-            cudaSuccess) {
+        if (cudaHostAlloc(reinterpret_cast<void**>(&host), kMaxStatusDevices * sizeof(int),
+                          cudaHostAllocMapped | cudaHostAllocPortable) != cudaSuccess) {
             cudaGetLastError();
             host = nullptr;
             return;
         }
-        *host = 0;
+        for (int i = 0; i < kMaxStatusDevices; ++i) host[i] = 0;
         if (cudaHostGetDevicePointer(reinterpret_cast<void**>(&dev), host, 0) != cudaSuccess) {
             cudaGetLastError();
             dev = nullptr;
@@ -711,6 +714,17 @@ int* ErrorWordDevicePtr(int** host_view) {
     });
     if (host_view != nullptr) *host_view = host;
     return dev;
+}
+
+// Device-side address of the current device's word (nullptr when the mapping could not be made).
+int* ErrorWordForCurrentDevice() {
+    int device = 0;
+    if (cudaGetDevice(&device) != cudaSuccess) {
+        cudaGetLastError();
+        return nullptr;
+    }
+    int* dev = ErrorWords(nullptr);
+    return (dev != nullptr && device >= 0 && device < kMaxStatusDevices) ? dev + device : nullptr;
 }
 
 // A packed variable-length batch: host offsets and a device scratch area for the work list.
@@ -784,14 +798,7 @@ int LaunchFlash(const ScaFlashFwdParams& f, cudaStream_t stream, const VarlenWor
     FlashKernelParams p{};
     p.out = f.out;
     p.lse = f.return_lse ? f.lse : nullptr;
-    int* host_word = nullptr;
-    p.error_word = ErrorWordDevicePtr(&host_word);
-    if (host_word != nullptr && *host_word != 0) {
-        const int code = *host_word;
-        *host_word = 0;
-        return Fail(SCA_CUDA_ERROR, "flash attention: an earlier launch gave up waiting on a barrier (role " +
-                                        std::to_string(code) + "); its output is invalid");
-    }
+    p.error_word = ErrorWordForCurrentDevice();
     p.seq_q = static_cast<int>(f.seq_q);
     p.seq_kv = static_cast<int>(f.seq_kv);
     p.heads = static_cast<int>(f.num_heads);
@@ -823,7 +830,16 @@ int LaunchFlash(const ScaFlashFwdParams& f, cudaStream_t stream, const VarlenWor
         if (int rc = EnsureDynamicSmem(fn, G::kSmemBytes, "flash_fwd_sm100_kernel")) return rc;
         flash_fwd_sm100_kernel<T, DP, QT, BN, false><<<grid, kFlashThreads, G::kSmemBytes, stream>>>(map_q, map_k, map_v, p);
     }
-    return CheckLaunch("flash_fwd_sm100_kernel", stream);
+    if (int rc = CheckLaunch("flash_fwd_sm100_kernel", stream)) return rc;
+    // With SCI_ATTENTION_DEBUG_SYNC=1 CheckLaunch has waited for the kernel: a wait that ran out is known now.
+    if (DebugSyncEnabled()) {
+        int device = 0, code = 0;
+        if (cudaGetDevice(&device) == cudaSuccess && sca_flash_status(device, &code) == SCA_OK && code != 0) {
+            return Fail(SCA_CUDA_ERROR, "flash attention: the launch gave up waiting on a barrier (role " +
+                                            std::to_string(code) + "); its output is invalid");
+        }
+    }
+    return SCA_OK;
 }
 
 int ValidateFlash(const ScaFlashFwdParams* params) {
@@ -872,6 +888,18 @@ int LaunchFlashTyped(const ScaFlashFwdParams& f, cudaStream_t stream, const Varl
 }  // namespace sca_b200
 
 using namespace sca_b200;
+
+extern "C" int sca_flash_status(int device_id, int32_t* status_out) {
+    if (status_out == nullptr) return Fail(SCA_INVALID_ARGUMENT, "flash status: null output");
+    if (device_id < 0 || device_id >= kMaxStatusDevices) {
+        return Fail(SCA_INVALID_ARGUMENT, "flash status: device index " + std::to_string(device_id) + " is out of range");
+    }
+    int* host = nullptr;
+    ErrorWords(&host);
+    // the kernel writes the word over the bus with a plain store; the host takes it with one atomic exchange
+    *status_out = host != nullptr ? __atomic_exchange_n(host + device_id, 0, __ATOMIC_ACQ_REL) : 0;
+    return SCA_OK;
+}
 
 extern "C" long long sca_flash_smem_bytes_for(int head_dim, long long elem_bytes, int block_m, int block_n,
                                               int stages) {

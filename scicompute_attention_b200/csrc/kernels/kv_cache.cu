@@ -118,6 +118,55 @@ int CheckShape(const ScaKvCacheShape* shape, int64_t elem_bytes, const char* wha
     return SCA_OK;
 }
 
+// Block-id lists are documented as device memory, but the reference's own PagedKVCache::ResetSeq hands
+// KVCache::Reset the ids straight out of a std::vector (src/kv_cache/paged_kv_cache.cpp:150-156), which only
+// works where the GPU can read pageable host memory. A list that lives in host memory is therefore copied into
+// a stream-ordered temporary first (the copy out of pageable memory completes before the call returns, so the
+// caller may drop its vector right away); device and managed pointers are used as they are.
+class StagedIds {
+public:
+    StagedIds() = default;
+    StagedIds(const StagedIds&) = delete;
+    StagedIds& operator=(const StagedIds&) = delete;
+    ~StagedIds() {
+        if (staged_ != nullptr && cudaFreeAsync(staged_, stream_) != cudaSuccess) cudaGetLastError();
+    }
+    int Stage(const int32_t* ids, int64_t count, cudaStream_t stream, const char* what) {
+        ids_ = ids;
+        cudaPointerAttributes attr{};
+        if (cudaPointerGetAttributes(&attr, ids) != cudaSuccess) {
+            cudaGetLastError();
+            return SCA_OK;  // no usable device: the launch below reports it
+        }
+        if (attr.type == cudaMemoryTypeDevice || attr.type == cudaMemoryTypeManaged) return SCA_OK;
+        if (attr.type == cudaMemoryTypeHost && attr.devicePointer != nullptr) {
+            ids_ = static_cast<const int32_t*>(attr.devicePointer);  // pinned and mapped: readable in place
+            return SCA_OK;
+        }
+        const size_t bytes = static_cast<size_t>(count) * sizeof(int32_t);
+        stream_ = stream;
+        cudaError_t err = cudaMallocAsync(reinterpret_cast<void**>(&staged_), bytes, stream);
+        if (err != cudaSuccess) {
+            staged_ = nullptr;
+            cudaGetLastError();
+            return FailCuda(err, what);
+        }
+        err = cudaMemcpyAsync(staged_, ids, bytes, cudaMemcpyHostToDevice, stream);
+        if (err != cudaSuccess) {
+            cudaGetLastError();
+            return FailCuda(err, what);
+        }
+        ids_ = staged_;
+        return SCA_OK;
+    }
+    const int32_t* get() const { return ids_; }
+
+private:
+    const int32_t* ids_{nullptr};
+    int32_t* staged_{nullptr};
+    cudaStream_t stream_{nullptr};
+};
+
 }  // namespace
 }  // namespace sca_b200
 
@@ -193,6 +242,9 @@ extern "C" int sca_launch_kv_reset_block(void* layer_k, void* layer_v, const int
     if (num_blocks <= 0) return SCA_OK;
     if (int rc = CheckShape(shape, elem_bytes, "kv reset")) return rc;
     cudaStream_t s = static_cast<cudaStream_t>(stream);
+    StagedIds ids;
+    if (int rc = ids.Stage(block_ids, num_blocks, s, "kv reset: staging host block ids")) return rc;
+    block_ids = ids.get();
     const int64_t block_bytes = shape->block_size * shape->num_kv_heads * shape->head_dim * elem_bytes;
     if (block_bytes % 16 == 0 && Aligned16(layer_k) && Aligned16(layer_v)) {
         const int64_t bv = block_bytes / 16;
@@ -217,6 +269,9 @@ extern "C" int sca_launch_kv_gather(const void* layer, const int32_t* block_ids,
     if (num_blocks <= 0) return SCA_OK;
     if (int rc = CheckShape(shape, elem_bytes, "kv gather")) return rc;
     cudaStream_t s = static_cast<cudaStream_t>(stream);
+    StagedIds ids;
+    if (int rc = ids.Stage(block_ids, num_blocks, s, "kv gather: staging host block ids")) return rc;
+    block_ids = ids.get();
     const int64_t block_bytes = shape->block_size * shape->num_kv_heads * shape->head_dim * elem_bytes;
     if (block_bytes % 16 == 0 && Aligned16(layer) && Aligned16(out)) {
         const int64_t bv = block_bytes / 16;

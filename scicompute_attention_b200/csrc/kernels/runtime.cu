@@ -25,6 +25,8 @@ bool DebugSync() {
 
 }  // namespace
 
+bool DebugSyncEnabled() { return DebugSync(); }
+
 int Fail(int code, const std::string& message) {
     g_last_error = message;
     return code;

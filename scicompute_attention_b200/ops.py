@@ -312,6 +312,15 @@ def _alloc_out(q, layout, return_lse):
     return out, lse
 
 
+def flash_status(device=None) -> int:
+    """0 when every flash launch on `device` so far ran to completion, otherwise 1 + the warp whose bounded wait ran
+    out (that launch's output is invalid). Synchronise the stream first; reading clears the record."""
+    index = torch.cuda.current_device() if device is None else torch.device(device).index
+    code = C.c_int32(0)
+    check(lib().sca_flash_status(int(index or 0), C.byref(code)))
+    return int(code.value)
+
+
 def flash_attention(q, k, v, *, causal=False, scale=None, return_lse=False, layout="bhsd", stream=None,
                     out=None, lse=None):
     """tcgen05 flash prefill (sca::flash_attention); fp16 / bf16 only."""
@@ -363,6 +372,19 @@ def simt_attention(q, k, v, *, causal=False, scale=None, return_lse=False, layou
     out, lse = _alloc_out(q, layout, return_lse)
     p = _fwd_params(q, k, v, out, lse, causal, scale, layout)
     check(lib().sca_launch_simt_forward(C.byref(p), _stream_ptr(stream)))
+    return (out, lse) if return_lse else out
+
+
+def naive_attention(q, k, v, *, causal=False, scale=None, return_lse=False, layout="bhsd", stream=None):
+    """Level-1 attention with the fp32 score matrix materialised in scratch (sca::naive_attention)."""
+    _require_cuda(q, k, v)
+    out, lse = _alloc_out(q, layout, return_lse)
+    p = _fwd_params(q, k, v, out, lse, causal, scale, layout)
+    need = lib().sca_naive_score_bytes(p.batch, p.num_heads, p.seq_q, p.seq_kv)
+    if need <= 0:
+        raise _lib.ScaError(4, "naive attention: invalid geometry")
+    scores = acquire_scratch_fp32(need // 4, q.device)
+    check(lib().sca_launch_naive_forward(C.byref(p), scores.data_ptr(), _stream_ptr(stream)))
     return (out, lse) if return_lse else out
 
 

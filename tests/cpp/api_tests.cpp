@@ -9,7 +9,10 @@
 #include <memory>
 #include <numeric>
 
+#include <cuda_runtime_api.h>
+
 #include "device/cuda_device.hpp"
+#include "device/stream.hpp"
 #include "mini_test.hpp"
 #include "scicompute_attention/attention.hpp"
 
@@ -467,6 +470,40 @@ TEST(Flash, GqaWithDifferentLengthsLseAndFp32Rejection) {
     EXPECT_HAS(rejected.error().message(), "naive");
 }
 
+// A cudaStreamNonBlocking stream does not synchronise with the legacy default stream. Outputs are allocated (and
+// zero-filled) per call and freed when the result goes out of scope, so repeated calls recycle the same pool blocks:
+// if allocation, fill or release were ordered on another stream than the kernel, some repetition would read zeros
+// or stale data.
+TEST(Streams, FlashAndDecodeOnANonBlockingStream) {
+    if (!Gpu()) SKIP_TEST("no CUDA device");
+    cudaStream_t raw = nullptr;
+    ASSERT_TRUE(cudaStreamCreateWithFlags(&raw, cudaStreamNonBlocking) == cudaSuccess);
+    sci::Stream stream(raw);
+    uint32_t seed = 47000;
+    for (int rep = 0; rep < 12; ++rep) {
+        sca::AttentionConfig cfg;
+        cfg.stream = &stream;
+        AttnCase f;
+        f.causal = true;
+        f.hq = 8;
+        f.hkv = 2;
+        f.sq = f.skv = 512;
+        f.seed = seed++;
+        if (!RunCase("flash(non-blocking stream)", sca::flash_attention, f, cfg)) break;
+        AttnCase d;
+        d.dtype = DType::kBFloat16;
+        d.batch = 4;
+        d.hq = 8;
+        d.hkv = 2;
+        d.sq = 1;
+        d.skv = 1500;
+        d.seed = seed++;
+        if (!RunCase("decode(non-blocking stream)", static_cast<Runner>(sca::decode_attention), d, cfg)) break;
+    }
+    cudaStreamSynchronize(raw);
+    cudaStreamDestroy(raw);
+}
+
 TEST(Flash, VarlenPackedBatches) {
     auto dev = Gpu();
     if (!dev) SKIP_TEST("no CUDA device");
@@ -772,6 +809,46 @@ TEST(PagedKv, IsolationExhaustionResetAndAttention) {
     EXPECT_FALSE(sca::paged_attention(wrong, cache, params, {}).ok());
 }
 
+// The short form sca::paged_attention(q, kv, cfg) takes table and lengths from the cache. With a length that is not
+// a multiple of block_size the zero-filled rest of the last block must carry no weight: the result equals the
+// explicit form with the cache's lengths.
+TEST(PagedKv, ShortFormUsesTheCachesOwnLengths) {
+    auto dev = Gpu();
+    if (!dev) SKIP_TEST("no CUDA device");
+    sca::KVCacheConfig cfg;
+    cfg.num_layers = 1;
+    cfg.num_kv_heads = 1;
+    cfg.head_dim = 32;
+    cfg.block_size = 8;
+    cfg.num_blocks = 8;
+    cfg.max_num_seqs = 2;
+    auto created = sca::PagedKVCache::Create(cfg, *dev);
+    ASSERT_TRUE(created.ok());
+    sca::PagedKVCache cache = std::move(*created);
+    auto tokens = [&](int64_t n, uint32_t seed) {
+        return ToDevice({n, 1, 32}, cfg.dtype, Encode(RandomFloats(size_t(n * 32), seed, 0.5f, 2.0f), cfg.dtype).bytes, *dev);
+    };
+    sci::Tensor t11 = tokens(11, 31), t5 = tokens(5, 32);
+    ASSERT_TRUE(cache.AppendTokens(0, 0, t11, t11, nullptr).ok());
+    ASSERT_TRUE(cache.AppendTokens(1, 0, t5, t5, nullptr).ok());
+    ASSERT_TRUE(cache.SyncPageTable(nullptr).ok());
+    sci::Tensor q = ToDevice({2, 2, 1, 32}, cfg.dtype, Encode(RandomFloats(2 * 2 * 32, 33), cfg.dtype).bytes, *dev);
+    sca::PagedAttentionParams params;
+    params.seq_lens = cache.SeqLensDevicePtr();
+    params.num_seqs = 2;
+    params.block_size = cache.BlockSize();  // the struct's default is 16, as in the reference
+    const auto explicit_form = sca::paged_attention(q, cache, params, {});
+    const auto short_form = sca::paged_attention(q, cache, sca::AttentionConfig{});
+    ASSERT_TRUE(explicit_form.ok());
+    ASSERT_TRUE(short_form.ok());
+    dev->synchronize();
+    const std::vector<float> a = ReadFloats(explicit_form->out), b = ReadFloats(short_form->out);
+    ASSERT_EQ(a.size(), b.size());
+    for (size_t i = 0; i < a.size(); ++i) EXPECT_EQ(a[i], b[i]);
+    // all values are >= 0.5, so an output row is >= 0.5 too unless zero rows were averaged in
+    for (float x : b) EXPECT_GE(x, 0.49f);
+}
+
 TEST(PagedKv, LaunchOrderIsLongestFirstAndOnlyOfferedWhenItIsAPermutation) {
     auto dev = Gpu();
     if (!dev) SKIP_TEST("no CUDA device");
@@ -813,6 +890,7 @@ TEST(PagedKv, LaunchOrderIsLongestFirstAndOnlyOfferedWhenItIsAPermutation) {
     sca::PagedAttentionParams params;
     params.seq_lens = cache.SeqLensDevicePtr();
     params.num_seqs = 3;
+    params.block_size = cache.BlockSize();
     const auto all = sca::paged_attention(q, cache, params, {});
     ASSERT_TRUE(all.ok());
     const std::vector<float> got = ReadFloats(all->out);

@@ -112,8 +112,8 @@ ScaDecodeFwdParams CopyDecode(const DecodeFwdParams& p) {
     return c;
 }
 
-// NaiveFwdParams and TiledFwdParams carry the same fields as the flash block (plus a score workspace the SIMT
-// kernel does not need); both go to sca_launch_simt_forward.
+// NaiveFwdParams and TiledFwdParams carry the same fields as the flash block (NaiveFwdParams adds the score
+// workspace, passed separately).
 template <typename P>
 ScaFlashFwdParams CopyStridedForward(const P& p, int32_t dtype_id) {
     ScaFlashFwdParams c{};
@@ -200,7 +200,7 @@ sci::Status LaunchPagedAttention(const PagedDecodeParams& p, sci::Stream* stream
 
 sci::Status LaunchNaiveForward(const NaiveFwdParams& p, sci::Stream* stream) {
     const ScaFlashFwdParams c = CopyStridedForward(p, static_cast<int32_t>(p.dtype));
-    return FromCode(sca_launch_simt_forward(&c, Handle(stream)));
+    return FromCode(sca_launch_naive_forward(&c, p.scores, Handle(stream)));
 }
 
 sci::Status LaunchTiledForward(const TiledFwdParams& p, sci::Stream* stream, int32_t, int32_t, int32_t) {

@@ -92,6 +92,7 @@ def test_python_ops_refuse_cpu_tensors():
     for call in (lambda: ops.flash_attention(k, k, k),
                  lambda: ops.flash_attention_varlen(packed, packed, packed, [0, 8], [0, 8]),
                  lambda: ops.simt_attention(k, k, k),
+                 lambda: ops.naive_attention(k, k, k),
                  lambda: ops.decode_partials(q, k, k),
                  lambda: ops.decode_triples(q, k, k),
                  lambda: ops.paged_attention(q, torch.zeros(4, 2, 2, 64, dtype=torch.float16),

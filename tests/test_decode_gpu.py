@@ -97,6 +97,23 @@ def test_ragged_seq_lens_and_empty_sequence():
         H.check_close(got[i:i + 1], expect, dt, f"ragged seq {i} len {n}")
 
 
+def test_seq_lens_beyond_the_kv_extent_are_clamped():
+    """A device length larger than S_kv must not read past the K/V tensors: the result is that of the full extent."""
+    import torch
+    from scicompute_attention_b200 import ops
+    dt, b, hq, hkv, skv, d = ol.DT_F16, 2, 8, 2, 300, 64
+    qb, qd = H.uniform_inputs((b, hq, 1, d), 77100, dt)
+    kb, kd = H.uniform_inputs((b, hkv, skv, d), 77101, dt)
+    vb, vd = H.uniform_inputs((b, hkv, skv, d), 77102, dt)
+    q, k, v = H.to_device(qb, dt), H.to_device(kb, dt), H.to_device(vb, dt)
+    lens = torch.tensor([skv + 1000, 123], dtype=torch.int32, device="cuda")
+    out = ops.decode_attention(q, k, v, num_splits=3, seq_lens=lens)
+    clamped = ops.decode_attention(q, k, v, num_splits=3, seq_lens=torch.tensor([skv, 123], dtype=torch.int32, device="cuda"))
+    torch.cuda.synchronize()
+    assert torch.equal(out, clamped)
+    H.check_close(H.to_host_f32(out)[:1], ol.attention_f64(qd[:1], kd[:1], vd[:1], causal=True), dt, "clamped length")
+
+
 def test_multi_token_queries_are_rejected():
     import torch
     from scicompute_attention_b200 import _lib, ops

@@ -97,6 +97,16 @@ def test_long_rows_exercise_the_lazy_rescale():
     H.check_close(H.to_host_f32(out), ol.attention_f64(qd, kd, vd), dt, "large-spread logits")
 
 
+def test_flash_status_is_clean_after_normal_launches():
+    """Every wait in the kernel is bounded; sca_flash_status reports a launch that gave up. Healthy launches leave 0."""
+    import torch
+    from scicompute_attention_b200 import ops
+    ops.flash_status()  # drop whatever an earlier process phase left
+    run_flash(ol.DT_BF16, 1, 4, 2, 333, 333, 128, True, 51000)
+    torch.cuda.synchronize()
+    assert ops.flash_status() == 0
+
+
 def test_fp32_is_rejected_with_a_pointer_to_the_reference_backends():
     import torch
     from scicompute_attention_b200 import _lib, ops
@@ -114,11 +124,11 @@ def test_simt_reference_backend_matches_oracle_including_fp32():
         qb, qd = H.uniform_inputs((1, 4, sq, d), 68000, dt)
         kb, kd = H.uniform_inputs((1, 2, skv, d), 68001, dt)
         vb, vd = H.uniform_inputs((1, 2, skv, d), 68002, dt)
-        out, lse = ops.simt_attention(H.to_device(qb, dt), H.to_device(kb, dt), H.to_device(vb, dt), causal=causal,
-                                      return_lse=True)
         expect, elog = ol.attention_f64(qd, kd, vd, causal=causal, want_lse=True)
-        H.check_close(H.to_host_f32(out), expect, dt, f"simt dt={dt}")
-        assert np.abs(lse.cpu().numpy() - elog).max() <= 1e-3
+        for name, fn in (("simt", ops.simt_attention), ("naive", ops.naive_attention)):
+            out, lse = fn(H.to_device(qb, dt), H.to_device(kb, dt), H.to_device(vb, dt), causal=causal, return_lse=True)
+            H.check_close(H.to_host_f32(out), expect, dt, f"{name} dt={dt}")
+            assert np.abs(lse.cpu().numpy() - elog).max() <= 1e-3, name
 
 
 def test_packed_variable_length_batches_in_one_launch():

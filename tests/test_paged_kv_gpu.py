@@ -57,6 +57,43 @@ def test_append_gather_reset_round_trip_all_block_sizes():
             assert np.array_equal(lv.view(torch.uint8).cpu().numpy().reshape(-1), ev)
 
 
+def test_block_id_lists_in_host_memory_are_staged_not_dereferenced():
+    """The reference's PagedKVCache::ResetSeq passes KVCache::Reset the ids of a std::vector
+    (src/kv_cache/paged_kv_cache.cpp:150-156). Reset and gather must give the same bytes for a list in pageable or
+    pinned host memory as for the same list on the device - and must never read a host address from a kernel."""
+    import ctypes as C
+
+    import torch
+    from scicompute_attention_b200 import _lib, ops
+    nblk, bs, hkv, d = 6, 8, 2, 64
+    rng = np.random.default_rng(7)
+    lk = torch.from_numpy(rng.integers(1, 255, size=(nblk, bs, hkv, d * 2), dtype=np.uint8)).cuda().view(torch.float16)
+    lv = torch.from_numpy(rng.integers(1, 255, size=(nblk, bs, hkv, d * 2), dtype=np.uint8)).cuda().view(torch.float16)
+    lk = lk.view(nblk, bs, hkv, d)
+    lv = lv.view(nblk, bs, hkv, d)
+    ids = np.array([4, 1, -1, nblk], dtype=np.int32)
+    shape = _lib.KvCacheShape(nblk, bs, hkv, d)
+    want_gather = ops.kv_gather(lk, torch.from_numpy(ids).cuda())
+    for kind in ("pageable", "pinned"):
+        host = torch.from_numpy(ids.copy())
+        if kind == "pinned":
+            host = host.pin_memory()
+        out = torch.empty_like(want_gather)
+        _lib.check(_lib.lib().sca_launch_kv_gather(lk.data_ptr(), host.data_ptr(), ids.size, out.data_ptr(),
+                                                   C.byref(shape), 2, None))
+        torch.cuda.synchronize()
+        assert torch.equal(out.view(torch.uint8), want_gather.view(torch.uint8)), kind
+        k2, v2 = lk.clone(), lv.clone()
+        k3, v3 = lk.clone(), lv.clone()
+        ops.kv_reset(k2, v2, torch.from_numpy(ids).cuda())
+        _lib.check(_lib.lib().sca_launch_kv_reset_block(k3.data_ptr(), v3.data_ptr(), host.data_ptr(), ids.size,
+                                                        C.byref(shape), 2, None))
+        torch.cuda.synchronize()
+        assert torch.equal(k2.view(torch.uint8), k3.view(torch.uint8)) and torch.equal(v2.view(torch.uint8), v3.view(torch.uint8)), kind
+        assert int(k3[4].view(torch.uint8).max()) == 0 and int(k3[1].view(torch.uint8).max()) == 0
+        assert int(k3[0].view(torch.uint8).min()) > 0
+
+
 def build_paged_case(dt, lens, bs, hkv, d, nblk, seed, shuffle=True, unmap=()):
     """Allocates pages through the oracle's LIFO allocator after a seeded shuffle of its free list,
     fills K/V for every sequence, and returns host-side truth."""
