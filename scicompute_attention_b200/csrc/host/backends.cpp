@@ -627,23 +627,23 @@ sci::Result<AttentionResult> RunPaged(const sci::Tensor& q, const PagedKVCache& 
     const int64_t max_blocks = params.max_blocks_per_seq > 0 ? params.max_blocks_per_seq : kv.MaxBlocksPerSeq();
     const int64_t upper = kcfg.num_blocks * block_size;  // bound of any sequence; true lengths come from seq_lens
 
-    // split count: the cache object knows every sequence's length on the host - use the mean of the
-    // non-empty ones as the typical length; an explicit request wins
+    // slot count: the cache object knows every sequence's length on the host, which is what the kernel's schedule
+    // depends on (steps in total, steps of the longest sequence); without device lengths every sequence is scanned
+    // over the whole table row. An explicit request wins.
     int64_t splits;
     if (cfg.num_splits > 0) {
         splits = detail::Min<int64_t>(cfg.num_splits, tables::kDispatch.max_splits);
     } else {
-        int64_t total = 0, live = 0;
+        const int64_t units_per_seq = kcfg.num_kv_heads * ((heads / kcfg.num_kv_heads + 15) / 16);
+        const int64_t row_tokens = detail::Min<int64_t>(upper, max_blocks * block_size);
+        int64_t total_steps = 0, longest_steps = 0;
         for (int64_t s = 0; s < num_seqs; ++s) {
-            const int64_t n = kv.SeqLength(s);
-            if (n > 0) {
-                total += n;
-                ++live;
-            }
+            const int64_t n = params.seq_lens != nullptr ? kv.SeqLength(s) : row_tokens;
+            const int64_t steps = detail::Max<int64_t>(1, detail::CeilDiv<int64_t>(n, tables::kDecodeStepTokens));
+            total_steps += steps;
+            longest_steps = detail::Max(longest_steps, steps);
         }
-        const int64_t typical = live > 0 ? total / live : upper;
-        splits = tables::PagedSplitsFor(typical, num_seqs, kcfg.num_kv_heads, heads / kcfg.num_kv_heads,
-                                        DeviceCapability::ForDevice(0).sm_count);
+        splits = tables::SlotsForSchedule(total_steps * units_per_seq, longest_steps, DeviceCapability::ForDevice(0).sm_count);
     }
     const int64_t elements = tables::PartialElements(num_seqs, heads, splits, d);
     const sci::Result<float*> scratch =

@@ -59,37 +59,39 @@ __device__ __forceinline__ int SwizzleV(int row, int chunk) {
     return kSwizzle ? (chunk ^ (((row >> 1) & 3) << 1)) : chunk;
 }
 
+// Tokens one CTA consumes per step: every warp takes one 16-token tile.
+constexpr int kSpan = kWarps * kTile;
+
+// Length of sequence b as the kernel sees it (never past the K/V extent / the page table) and the number of
+// kSpan-token steps it takes. An empty sequence still counts one (empty) step so that somebody writes its partial.
+template <bool kPaged>
+__device__ __forceinline__ int64_t SeqLen(const ScaDecodeFwdParams& p, int64_t b) {
+    int64_t len = p.seq_lens != nullptr ? static_cast<int64_t>(__ldg(p.seq_lens + b)) : p.seq_kv;
+    if (len < 0) len = 0;
+    const int64_t cap = kPaged ? p.max_blocks_per_seq * p.block_size : p.seq_kv;
+    return len < cap ? len : cap;
+}
+__device__ __forceinline__ int64_t StepsFor(int64_t len) {
+    const int64_t t = (len + kSpan - 1) / kSpan;
+    return t > 0 ? t : 1;
+}
+
+// One segment = tokens [j_begin, j_end) of one (sequence, kv head, head chunk): streams K/V once, keeps the running
+// softmax state of up to 16 query heads, and writes one (m, l, O) partial per head into `slot`.
 template <typename T, int D, bool kPaged, bool kHi>
-__global__ void __launch_bounds__(kThreads)
-decode_partial_kernel(const ScaDecodeFwdParams p, const int head_chunks, const int32_t* __restrict__ seq_order) {
+__device__ __forceinline__ void DecodeSegment(const ScaDecodeFwdParams& p, unsigned char* smem, const int64_t b,
+                                              const int hk, const int hc, const int64_t j_begin, const int64_t j_end,
+                                              const int slot) {
     using G = DecodeGeom<D>;
     constexpr int CPR = G::kChunksPerRow;
-    extern __shared__ __align__(128) unsigned char smem[];
-
     const int lane = threadIdx.x & 31;
     const int warp = threadIdx.x >> 5;
     const int g = lane >> 2;  // fragment row / token slot
     const int c = lane & 3;   // fragment column pair
-
-    int64_t rest = blockIdx.x;
-    const int split = static_cast<int>(rest % p.num_splits);
-    rest /= p.num_splits;
-    const int hc = static_cast<int>(rest % head_chunks);
-    rest /= head_chunks;
-    const int hk = static_cast<int>(rest % p.num_kv_heads);
-    const int64_t b_slot = rest / p.num_kv_heads;
-    const int64_t b = seq_order != nullptr ? static_cast<int64_t>(__ldg(seq_order + b_slot)) : b_slot;
-    if (static_cast<uint64_t>(b) >= static_cast<uint64_t>(p.batch)) return;  // a hint that is no permutation
     const int group = static_cast<int>(p.num_heads / p.num_kv_heads);
     const int head0 = hk * group + hc * 16;
     const int nheads = min(16, group - hc * 16);
 
-    int64_t seq_len = p.seq_lens != nullptr ? static_cast<int64_t>(p.seq_lens[b]) : p.seq_kv;
-    if (seq_len < 0) seq_len = 0;
-    if (!kPaged && seq_len > p.seq_kv) seq_len = p.seq_kv;  // never read past the K/V extent
-    const int64_t chunk = (seq_len + p.num_splits - 1) / p.num_splits;
-    const int64_t j_begin = static_cast<int64_t>(split) * chunk;
-    const int64_t j_end = min(j_begin + chunk, seq_len);
     const int ntiles = j_end > j_begin ? static_cast<int>((j_end - j_begin + kTile - 1) / kTile) : 0;
     const int my_tiles = ntiles > warp ? (ntiles - warp + kWarps - 1) / kWarps : 0;
 
@@ -126,7 +128,7 @@ decode_partial_kernel(const ScaDecodeFwdParams p, const int head_chunks, const i
     // Issues the copies of this warp's `tl`-th tile into `stage`; returns the 16-bit token validity.
     auto issue = [&](int tl, int stage) -> uint32_t {
         const int64_t jt0 = j_begin + static_cast<int64_t>(warp + tl * kWarps) * kTile;
-        int prow = -1;
+        int prow = -1;  // row of the pool / the K/V slab; pools stay below 2^31 rows
         if (lane < kTile) {
             const int64_t jt = jt0 + lane;
             if (jt < j_end) {
@@ -337,11 +339,153 @@ decode_partial_kernel(const ScaDecodeFwdParams p, const int head_chunks, const i
             acc += wm[32 + row * D + d] * wgt;
             l_all += wm[16 + row] * wgt;
         }
-        const int64_t flat = (b * p.num_heads + head0 + row) * p.num_splits + split;
+        const int64_t flat = (b * p.num_heads + head0 + row) * p.num_splits + slot;
         p.partial_o[flat * D + d] = acc;
         if (d == 0) {
             p.partial_m[flat] = m_all * kLn2;  // stored in natural units like the reference workspace
             p.partial_l[flat] = l_all;
+        }
+    }
+    __syncthreads();  // the rings double as merge staging: nobody refills them before everyone has read
+}
+
+// Marks slots [first, num_splits) of every head of one (sequence, kv head, head chunk) as empty (m = -inf; the merge
+// skips such entries without reading l or O).
+__device__ __forceinline__ void MarkUnusedSlots(const ScaDecodeFwdParams& p, int64_t b, int hk, int hc, int first) {
+    const int group = static_cast<int>(p.num_heads / p.num_kv_heads);
+    const int head0 = hk * group + hc * 16;
+    const int nheads = min(16, group - hc * 16);
+    const int unused = static_cast<int>(p.num_splits) - first;
+    for (int item = threadIdx.x; item < nheads * unused; item += kThreads) {
+        const int row = item / unused;
+        const int slot = first + item % unused;
+        p.partial_m[(b * p.num_heads + head0 + row) * p.num_splits + slot] = -CUDART_INF_F;
+    }
+}
+
+// The split-K partial kernel, scheduled for an equal share of the K/V stream per CTA.
+//
+// The work is the list of kSpan-token steps of every (sequence, kv head, head chunk), sequence-major. The grid is one
+// wave of resident CTAs and CTA c takes steps [c * per_cta, (c + 1) * per_cta) of that list - a contiguous stretch that
+// may start and end in the middle of a sequence and may cover several short ones. Every piece of a sequence a CTA
+// holds is one "segment" and yields one partial; the pieces of one sequence sit in consecutive CTAs, so the segment's
+// slot in the [rows, num_splits] partial arrays is the distance to the first CTA that touches the sequence.
+// per_cta is never smaller than longest_sequence / (num_splits - 1) steps, which bounds the pieces of any sequence by
+// num_splits; slots that stay unused are marked empty by the CTA that holds the sequence's first step.
+// With num_splits == 1 a CTA takes whole (sequence, kv head, head chunk) units instead.
+// Sequence lengths are read on the device (seq_lens), so the schedule needs no host knowledge of a ragged batch.
+template <typename T, int D, bool kPaged, bool kHi>
+__global__ void __launch_bounds__(kThreads)
+decode_partial_kernel(const ScaDecodeFwdParams p, const int head_chunks) {
+    extern __shared__ __align__(128) unsigned char smem[];
+    __shared__ int64_t s_part[kWarps][2];
+    __shared__ int64_t s_found[2];
+    const int lane = threadIdx.x & 31;
+    const int warp = threadIdx.x >> 5;
+    const int64_t units_per_seq = p.num_kv_heads * head_chunks;  // (kv head, head chunk) pairs
+
+    if (p.num_splits == 1) {
+        const int64_t units = p.batch * units_per_seq;
+        const int64_t u0 = units * blockIdx.x / gridDim.x, u1 = units * (blockIdx.x + 1) / gridDim.x;
+        for (int64_t u = u0; u < u1; ++u) {
+            const int64_t b = u / units_per_seq;
+            const int gi = static_cast<int>(u % units_per_seq);
+            DecodeSegment<T, D, kPaged, kHi>(p, smem, b, gi / head_chunks, gi % head_chunks, 0, SeqLen<kPaged>(p, b), 0);
+        }
+        return;
+    }
+
+    // ---- pass 1: total steps and the longest sequence ----------------------------------------------
+    int64_t sum = 0, longest = 0;
+    for (int64_t b = threadIdx.x; b < p.batch; b += kThreads) {
+        const int64_t t = StepsFor(SeqLen<kPaged>(p, b));
+        sum += t;
+        longest = t > longest ? t : longest;
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+        sum += __shfl_xor_sync(0xffffffffu, sum, o);
+        const int64_t other = __shfl_xor_sync(0xffffffffu, longest, o);
+        longest = other > longest ? other : longest;
+    }
+    if (lane == 0) {
+        s_part[warp][0] = sum;
+        s_part[warp][1] = longest;
+    }
+    __syncthreads();
+    sum = 0;
+    longest = 0;
+#pragma unroll
+    for (int w = 0; w < kWarps; ++w) {
+        sum += s_part[w][0];
+        longest = s_part[w][1] > longest ? s_part[w][1] : longest;
+    }
+    const int64_t total = sum * units_per_seq;
+    int64_t per_cta = (total + gridDim.x - 1) / gridDim.x;
+    const int64_t by_slots = (longest + p.num_splits - 2) / (p.num_splits - 1);
+    if (per_cta < by_slots) per_cta = by_slots;
+    const int64_t begin = static_cast<int64_t>(blockIdx.x) * per_cta;
+    if (begin >= total) return;
+    const int64_t end = begin + per_cta < total ? begin + per_cta : total;
+
+    // ---- pass 2: the sequence that holds step `begin` ----------------------------------------------
+    // steps before sequence b: units_per_seq * before[b]; find b with before[b] <= begin / units_per_seq < before[b + 1]
+    const int64_t want = begin / units_per_seq;
+    int64_t running = 0;
+    __syncthreads();
+    for (int64_t base = 0; base < p.batch && running <= want; base += kThreads) {
+        const int64_t b = base + threadIdx.x;
+        const int64_t t = b < p.batch ? StepsFor(SeqLen<kPaged>(p, b)) : 0;
+        int64_t incl = t;
+#pragma unroll
+        for (int o = 1; o < 32; o <<= 1) {
+            const int64_t up = __shfl_up_sync(0xffffffffu, incl, o);
+            if (lane >= o) incl += up;
+        }
+        if (lane == 31) s_part[warp][0] = incl;
+        __syncthreads();
+        int64_t before = running + incl - t;
+        int64_t chunk_total = 0;
+#pragma unroll
+        for (int w = 0; w < kWarps; ++w) {
+            if (w < warp) before += s_part[w][0];
+            chunk_total += s_part[w][0];
+        }
+        if (t > 0 && before <= want && want < before + t) {
+            s_found[0] = b;
+            s_found[1] = before;
+        }
+        running += chunk_total;
+        __syncthreads();
+    }
+    int64_t b = s_found[0];
+    int64_t before = s_found[1];  // steps of one unit column before sequence b
+    int64_t len = SeqLen<kPaged>(p, b);
+    int64_t steps = StepsFor(len);
+
+    // ---- walk the stretch segment by segment --------------------------------------------------------
+    int64_t pos = begin;
+    while (pos < end) {
+        const int64_t in_seq = pos - units_per_seq * before;  // offset inside sequence b's steps
+        const int gi = static_cast<int>(in_seq / steps);
+        const int64_t t0 = in_seq % steps;
+        const int64_t unit_start = units_per_seq * before + gi * steps;
+        int64_t t1 = t0 + (end - pos);
+        if (t1 > steps) t1 = steps;
+        const int hk = gi / head_chunks, hc = gi % head_chunks;
+        const int slot = static_cast<int>(blockIdx.x - unit_start / per_cta);
+        if (t0 == 0) {
+            const int used = static_cast<int>((unit_start + steps - 1) / per_cta - unit_start / per_cta) + 1;
+            MarkUnusedSlots(p, b, hk, hc, used);
+        }
+        const int64_t j_end = t1 * kSpan < len ? t1 * kSpan : len;
+        DecodeSegment<T, D, kPaged, kHi>(p, smem, b, hk, hc, t0 * kSpan, j_end, slot);
+        pos += t1 - t0;
+        if (t1 == steps && gi == units_per_seq - 1 && pos < end) {
+            before += steps;
+            ++b;
+            len = SeqLen<kPaged>(p, b);
+            steps = StepsFor(len);
         }
     }
 }
@@ -398,43 +542,55 @@ decode_merge_kernel(const MergeSource src, const int64_t rows, const int parts, 
 }
 
 template <typename T, int D, bool kPaged, bool kHi>
-int LaunchPartial(const ScaDecodeFwdParams& p, int head_chunks, const int32_t* seq_order, cudaStream_t stream) {
+int LaunchPartial(const ScaDecodeFwdParams& p, int head_chunks, cudaStream_t stream) {
     using G = DecodeGeom<D>;
     const void* fn = reinterpret_cast<const void*>(&decode_partial_kernel<T, D, kPaged, kHi>);
     if (int rc = EnsureDynamicSmem(fn, G::kSmemBytes, "decode_partial_kernel")) return rc;
-    const int64_t blocks = p.batch * p.num_kv_heads * head_chunks * p.num_splits;
-    if (blocks <= 0 || blocks > 0x7fffffffLL) {
-        return Fail(SCA_INVALID_ARGUMENT, "decode: grid of " + std::to_string(blocks) + " blocks is out of range");
+    // one wave: as many CTAs as stay resident together, fewer when there is less work than that
+    static int resident_per_sm = 0;  // per instantiation; the same on every device of one model
+    if (resident_per_sm == 0) {
+        int n = 0;
+        if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&n, decode_partial_kernel<T, D, kPaged, kHi>, kThreads,
+                                                          G::kSmemBytes) != cudaSuccess || n < 1) {
+            cudaGetLastError();
+            n = 1;
+        }
+        resident_per_sm = n;
     }
+    const int64_t units = p.batch * p.num_kv_heads * head_chunks;
+    const int64_t upper = kPaged ? p.max_blocks_per_seq * p.block_size : p.seq_kv;
+    const int64_t steps = std::max<int64_t>(1, (std::min(p.seq_kv, upper) + kSpan - 1) / kSpan);
+    const int64_t work = p.num_splits == 1 ? units : units * steps;  // upper bound on the steps of the list
+    const int64_t blocks = std::max<int64_t>(1, std::min<int64_t>(static_cast<int64_t>(SmCount()) * resident_per_sm, work));
     decode_partial_kernel<T, D, kPaged, kHi>
-        <<<static_cast<unsigned>(blocks), kThreads, G::kSmemBytes, stream>>>(p, head_chunks, seq_order);
+        <<<static_cast<unsigned>(blocks), kThreads, G::kSmemBytes, stream>>>(p, head_chunks);
     return CheckLaunch("decode_partial_kernel", stream);
 }
 
 template <typename T, int D>
-int LaunchPartialForDim(const ScaDecodeFwdParams& p, const int32_t* seq_order, cudaStream_t stream) {
+int LaunchPartialForDim(const ScaDecodeFwdParams& p, cudaStream_t stream) {
     const int group = static_cast<int>(p.num_heads / p.num_kv_heads);
     const int head_chunks = (group + 15) / 16;
     const bool paged = p.page_table != nullptr;
     const bool hi = group > 8;
     if (paged) {
-        return hi ? LaunchPartial<T, D, true, true>(p, head_chunks, seq_order, stream)
-                  : LaunchPartial<T, D, true, false>(p, head_chunks, seq_order, stream);
+        return hi ? LaunchPartial<T, D, true, true>(p, head_chunks, stream)
+                  : LaunchPartial<T, D, true, false>(p, head_chunks, stream);
     }
-    return hi ? LaunchPartial<T, D, false, true>(p, head_chunks, seq_order, stream)
-              : LaunchPartial<T, D, false, false>(p, head_chunks, seq_order, stream);
+    return hi ? LaunchPartial<T, D, false, true>(p, head_chunks, stream)
+              : LaunchPartial<T, D, false, false>(p, head_chunks, stream);
 }
 
 template <typename T>
-int LaunchPartialTyped(const ScaDecodeFwdParams& p, const int32_t* seq_order, cudaStream_t stream) {
+int LaunchPartialTyped(const ScaDecodeFwdParams& p, cudaStream_t stream) {
     switch (p.head_dim) {
-        case 32: return LaunchPartialForDim<T, 32>(p, seq_order, stream);
-        case 64: return LaunchPartialForDim<T, 64>(p, seq_order, stream);
-        case 96: return LaunchPartialForDim<T, 96>(p, seq_order, stream);
-        case 128: return LaunchPartialForDim<T, 128>(p, seq_order, stream);
-        case 160: return LaunchPartialForDim<T, 160>(p, seq_order, stream);
-        case 192: return LaunchPartialForDim<T, 192>(p, seq_order, stream);
-        case 256: return LaunchPartialForDim<T, 256>(p, seq_order, stream);
+        case 32: return LaunchPartialForDim<T, 32>(p, stream);
+        case 64: return LaunchPartialForDim<T, 64>(p, stream);
+        case 96: return LaunchPartialForDim<T, 96>(p, stream);
+        case 128: return LaunchPartialForDim<T, 128>(p, stream);
+        case 160: return LaunchPartialForDim<T, 160>(p, stream);
+        case 192: return LaunchPartialForDim<T, 192>(p, stream);
+        case 256: return LaunchPartialForDim<T, 256>(p, stream);
         default: break;
     }
     return Fail(SCA_INVALID_ARGUMENT,
@@ -506,10 +662,10 @@ int LaunchMergeOut(const ScaDecodeFwdParams& p, cudaStream_t stream) {
 // fp32 inputs take the SIMT partial kernel (simt.cu); declared here, defined there.
 int LaunchDecodePartialF32(const ScaDecodeFwdParams& p, cudaStream_t stream);
 
-int LaunchDecodePartials(const ScaDecodeFwdParams& p, cudaStream_t stream, const int32_t* seq_order = nullptr) {
+int LaunchDecodePartials(const ScaDecodeFwdParams& p, cudaStream_t stream) {
     switch (p.dtype) {
-        case SCA_DTYPE_F16: return LaunchPartialTyped<__half>(p, seq_order, stream);
-        case SCA_DTYPE_BF16: return LaunchPartialTyped<__nv_bfloat16>(p, seq_order, stream);
+        case SCA_DTYPE_F16: return LaunchPartialTyped<__half>(p, stream);
+        case SCA_DTYPE_BF16: return LaunchPartialTyped<__nv_bfloat16>(p, stream);
         case SCA_DTYPE_F32: return LaunchDecodePartialF32(p, stream);
         default: break;
     }
@@ -599,7 +755,8 @@ extern "C" int sca_launch_paged_attention_ordered(const ScaPagedDecodeParams* pa
     }
     if (int rc = ValidateDecode(&p, true)) return rc;
     cudaStream_t s = static_cast<cudaStream_t>(stream);
-    if (int rc = LaunchDecodePartials(p, s, seq_order)) return rc;
+    (void)seq_order;  // the kernel deals out equal shares of the K/V stream itself; the hint has nothing left to improve
+    if (int rc = LaunchDecodePartials(p, s)) return rc;
     return LaunchMergeOut(p, s);
 }
 

@@ -53,7 +53,9 @@ int CheckLaunch(const char* kernel_name, cudaStream_t stream) {
 }
 
 int EnsureDynamicSmem(const void* kernel, size_t bytes, const char* kernel_name) {
-    if (bytes <= 48 * 1024) return SCA_OK;
+    // the 48 KiB default covers static + dynamic shared memory together: opt in early enough to leave room for a
+    // kernel's static variables
+    if (bytes <= 40 * 1024) return SCA_OK;
     static std::mutex mu;
     static std::unordered_map<const void*, size_t> granted;  // per (device, kernel) would be stricter;
     int device = 0;                                           // the key below folds the device in
@@ -67,7 +69,8 @@ int EnsureDynamicSmem(const void* kernel, size_t bytes, const char* kernel_name)
         cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(bytes));
     if (err != cudaSuccess) {
         cudaGetLastError();
-        return FailCuda(err, kernel_name);
+        return FailCuda(err, (std::string("cudaFuncSetAttribute(") + kernel_name + ", dynamic shared memory " +
+                              std::to_string(bytes) + " B)").c_str());
     }
     granted[key] = bytes;
     return SCA_OK;

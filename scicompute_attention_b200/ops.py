@@ -18,7 +18,6 @@ from ._lib import (DTYPE_BF16, DTYPE_F16, DTYPE_F32, DecodeFwdParams, DecodeStri
                    KvCacheShape, PagedDecodeParams, check, lib)
 
 MAX_SPLITS = 64          # upper bound of the automatic split count on B200
-MIN_TOKENS_PER_SPLIT = 256
 
 _DTYPE_IDS = {torch.float32: DTYPE_F32, torch.float16: DTYPE_F16, torch.bfloat16: DTYPE_BF16}
 _scratch: dict[tuple[int, int], torch.Tensor] = {}
@@ -65,26 +64,40 @@ def acquire_scratch_fp32(elements: int, device: torch.device, kind: int = 1) -> 
     return cur
 
 
+DECODE_STEP_TOKENS = 64  # tokens one CTA of the decode kernel consumes per step (4 warps x 16)
+
+
+def slots_for_schedule(total_steps: int, longest_steps: int, sms: int) -> int:
+    """Partial slots per row for the decode kernel's schedule: one wave of resident CTAs (2 per SM), each with an
+    equal, contiguous share of the 64-token steps of all (sequence, kv head, head chunk) units; a unit cut by CTA
+    boundaries yields one partial per piece. Needed: the pieces of the longest unit, plus one for a share that starts
+    in its middle. (The reference's rule, one CTA per fixed split, is ceil(seq_kv / 512) capped at 16:
+    src/backends/decode/decode_config.hpp:24-31.)"""
+    if total_steps <= 0 or longest_steps <= 1:
+        return 1
+    ctas = 2 * (sms if sms > 0 else 148)
+    per_cta = max(1, -(-total_steps // ctas))
+    return max(2, min(-(-longest_steps // per_cta) + 1, MAX_SPLITS))
+
+
 def splits_for(seq_kv: int, batch: int, num_kv_heads: int, group: int, sms: int) -> int:
-    """Automatic split-K count on B200: enough CTAs for ~4 waves of 2 resident CTAs per SM, but never
-    fewer than MIN_TOKENS_PER_SPLIT tokens per split (the reference's rule, written for 36 SMs, is
-    ceil(seq_kv / 512) capped at 16: src/backends/decode/decode_config.hpp:24-31)."""
+    """Automatic slot count for equally long sequences."""
     if seq_kv <= 0:
         return 1
-    head_chunks = (group + 15) // 16
-    base_ctas = max(1, batch * num_kv_heads * head_chunks)
-    want = -(-(sms * 2 * 4) // base_ctas)
-    by_len = max(1, seq_kv // MIN_TOKENS_PER_SPLIT)
-    return max(1, min(want, by_len, MAX_SPLITS))
+    units = max(1, batch * num_kv_heads * ((group + 15) // 16))
+    steps = -(-seq_kv // DECODE_STEP_TOKENS)
+    return slots_for_schedule(units * steps, steps, sms)
 
 
-def paged_splits_for(typical_len: int, num_seqs: int, num_kv_heads: int, group: int, sms: int) -> int:
-    """Split count for ragged paged batches: every sequence gets the same number of splits, each
-    covering ceil(len / splits) of its tokens, so CTA work is proportional to the sequence length.
-    About 2048 tokens per split keeps the longest CTA short enough for the tail of the grid while
-    amortising the per-CTA prologue and the merge; never fewer splits than the contiguous rule asks for."""
-    by_balance = max(1, min(16, (typical_len + 1024) // 2048))
-    return max(by_balance, splits_for(typical_len, num_seqs, num_kv_heads, group, sms))
+def paged_splits_for(typical_len: int, num_seqs: int, num_kv_heads: int, group: int, sms: int, longest_len: int = 0) -> int:
+    """Slot count for a ragged batch of mean length `typical_len`; the longest sequence is taken as twice the mean
+    unless `longest_len` says otherwise."""
+    if typical_len <= 0:
+        return 1
+    units = max(1, num_seqs * num_kv_heads * ((group + 15) // 16))
+    steps = -(-typical_len // DECODE_STEP_TOKENS)
+    longest = -(-longest_len // DECODE_STEP_TOKENS) if longest_len > 0 else 2 * steps
+    return slots_for_schedule(units * steps, longest, sms)
 
 
 def _strides(layout: str, seq: int, heads: int, d: int) -> tuple[int, int, int]:
