@@ -385,6 +385,7 @@ decode_partial_kernel(const ScaDecodeFwdParams p, const int head_chunks) {
     const int64_t units_per_seq = p.num_kv_heads * head_chunks;  // (kv head, head chunk) pairs
 
     if (p.num_splits == 1) {
+        asm volatile("griddepcontrol.launch_dependents;\n" ::: "memory");
         const int64_t units = p.batch * units_per_seq;
         const int64_t u0 = units * blockIdx.x / gridDim.x, u1 = units * (blockIdx.x + 1) / gridDim.x;
         for (int64_t u = u0; u < u1; ++u) {
@@ -395,73 +396,91 @@ decode_partial_kernel(const ScaDecodeFwdParams p, const int head_chunks) {
         return;
     }
 
-    // ---- pass 1: total steps and the longest sequence ----------------------------------------------
-    int64_t sum = 0, longest = 0;
-    for (int64_t b = threadIdx.x; b < p.batch; b += kThreads) {
-        const int64_t t = StepsFor(SeqLen<kPaged>(p, b));
-        sum += t;
-        longest = t > longest ? t : longest;
-    }
-#pragma unroll
-    for (int o = 16; o > 0; o >>= 1) {
-        sum += __shfl_xor_sync(0xffffffffu, sum, o);
-        const int64_t other = __shfl_xor_sync(0xffffffffu, longest, o);
-        longest = other > longest ? other : longest;
-    }
-    if (lane == 0) {
-        s_part[warp][0] = sum;
-        s_part[warp][1] = longest;
-    }
-    __syncthreads();
-    sum = 0;
-    longest = 0;
-#pragma unroll
-    for (int w = 0; w < kWarps; ++w) {
-        sum += s_part[w][0];
-        longest = s_part[w][1] > longest ? s_part[w][1] : longest;
-    }
-    const int64_t total = sum * units_per_seq;
-    int64_t per_cta = (total + gridDim.x - 1) / gridDim.x;
-    const int64_t by_slots = (longest + p.num_splits - 2) / (p.num_splits - 1);
-    if (per_cta < by_slots) per_cta = by_slots;
-    const int64_t begin = static_cast<int64_t>(blockIdx.x) * per_cta;
-    if (begin >= total) return;
-    const int64_t end = begin + per_cta < total ? begin + per_cta : total;
-
-    // ---- pass 2: the sequence that holds step `begin` ----------------------------------------------
-    // steps before sequence b: units_per_seq * before[b]; find b with before[b] <= begin / units_per_seq < before[b + 1]
-    const int64_t want = begin / units_per_seq;
-    int64_t running = 0;
-    __syncthreads();
-    for (int64_t base = 0; base < p.batch && running <= want; base += kThreads) {
-        const int64_t b = base + threadIdx.x;
-        const int64_t t = b < p.batch ? StepsFor(SeqLen<kPaged>(p, b)) : 0;
-        int64_t incl = t;
-#pragma unroll
-        for (int o = 1; o < 32; o <<= 1) {
-            const int64_t up = __shfl_up_sync(0xffffffffu, incl, o);
-            if (lane >= o) incl += up;
+    int64_t b, before, len, steps, per_cta, begin, end;
+    if (p.seq_lens == nullptr) {
+        // every sequence has the same length: the list is regular and needs no look at device memory
+        len = SeqLen<kPaged>(p, 0);
+        steps = StepsFor(len);
+        const int64_t total = p.batch * steps * units_per_seq;
+        per_cta = (total + gridDim.x - 1) / gridDim.x;
+        const int64_t by_slots = (steps + p.num_splits - 2) / (p.num_splits - 1);
+        if (per_cta < by_slots) per_cta = by_slots;
+        begin = static_cast<int64_t>(blockIdx.x) * per_cta;
+        if (begin >= total) return;
+        end = begin + per_cta < total ? begin + per_cta : total;
+        b = begin / (steps * units_per_seq);
+        before = b * steps;
+    } else {
+        // ---- pass 1: total steps and the longest sequence ------------------------------------------
+        int64_t sum = 0, longest = 0;
+        for (int64_t i = threadIdx.x; i < p.batch; i += kThreads) {
+            const int64_t t = StepsFor(SeqLen<kPaged>(p, i));
+            sum += t;
+            longest = t > longest ? t : longest;
         }
-        if (lane == 31) s_part[warp][0] = incl;
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) {
+            sum += __shfl_xor_sync(0xffffffffu, sum, o);
+            const int64_t other = __shfl_xor_sync(0xffffffffu, longest, o);
+            longest = other > longest ? other : longest;
+        }
+        if (lane == 0) {
+            s_part[warp][0] = sum;
+            s_part[warp][1] = longest;
+        }
         __syncthreads();
-        int64_t before = running + incl - t;
-        int64_t chunk_total = 0;
+        sum = 0;
+        longest = 0;
 #pragma unroll
         for (int w = 0; w < kWarps; ++w) {
-            if (w < warp) before += s_part[w][0];
-            chunk_total += s_part[w][0];
+            sum += s_part[w][0];
+            longest = s_part[w][1] > longest ? s_part[w][1] : longest;
         }
-        if (t > 0 && before <= want && want < before + t) {
-            s_found[0] = b;
-            s_found[1] = before;
-        }
-        running += chunk_total;
+        const int64_t total = sum * units_per_seq;
+        per_cta = (total + gridDim.x - 1) / gridDim.x;
+        const int64_t by_slots = (longest + p.num_splits - 2) / (p.num_splits - 1);
+        if (per_cta < by_slots) per_cta = by_slots;
+        begin = static_cast<int64_t>(blockIdx.x) * per_cta;
+        if (begin >= total) return;
+        end = begin + per_cta < total ? begin + per_cta : total;
+
+        // ---- pass 2: the sequence that holds step `begin` ------------------------------------------
+        // steps before sequence i: units_per_seq * before[i]; find i with before[i] <= begin / units_per_seq < before[i + 1]
+        const int64_t want = begin / units_per_seq;
+        int64_t running = 0;
         __syncthreads();
+        for (int64_t base = 0; base < p.batch && running <= want; base += kThreads) {
+            const int64_t i = base + threadIdx.x;
+            const int64_t t = i < p.batch ? StepsFor(SeqLen<kPaged>(p, i)) : 0;
+            int64_t incl = t;
+#pragma unroll
+            for (int o = 1; o < 32; o <<= 1) {
+                const int64_t up = __shfl_up_sync(0xffffffffu, incl, o);
+                if (lane >= o) incl += up;
+            }
+            if (lane == 31) s_part[warp][0] = incl;
+            __syncthreads();
+            int64_t mine = running + incl - t;
+            int64_t chunk_total = 0;
+#pragma unroll
+            for (int w = 0; w < kWarps; ++w) {
+                if (w < warp) mine += s_part[w][0];
+                chunk_total += s_part[w][0];
+            }
+            if (t > 0 && mine <= want && want < mine + t) {
+                s_found[0] = i;
+                s_found[1] = mine;
+            }
+            running += chunk_total;
+            __syncthreads();
+        }
+        b = s_found[0];
+        before = s_found[1];  // steps of one unit column before sequence b
+        len = SeqLen<kPaged>(p, b);
+        steps = StepsFor(len);
     }
-    int64_t b = s_found[0];
-    int64_t before = s_found[1];  // steps of one unit column before sequence b
-    int64_t len = SeqLen<kPaged>(p, b);
-    int64_t steps = StepsFor(len);
+    // the merge kernel that follows on the stream may be set up while this grid streams K/V
+    asm volatile("griddepcontrol.launch_dependents;\n" ::: "memory");
 
     // ---- walk the stretch segment by segment --------------------------------------------------------
     int64_t pos = begin;
@@ -507,6 +526,9 @@ template <typename T, bool kTriples>
 __global__ void __launch_bounds__(256)
 decode_merge_kernel(const MergeSource src, const int64_t rows, const int parts, const int head_dim,
                     void* __restrict__ out, const int64_t heads, const int64_t o_sb, const int64_t o_sh) {
+    // launched with programmatic stream serialisation: the grid may start before the kernel that produces the parts
+    // has finished; this returns once that kernel is complete and its writes are visible (a no-op otherwise)
+    asm volatile("griddepcontrol.wait;\n" ::: "memory");
     const int64_t total = rows * head_dim;
     for (int64_t item = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x; item < total;
          item += static_cast<int64_t>(gridDim.x) * blockDim.x) {
@@ -539,6 +561,25 @@ decode_merge_kernel(const MergeSource src, const int64_t rows, const int parts, 
             reinterpret_cast<T*>(out)[b * o_sb + h * o_sh + d] = FromFloat<T>(acc * inv);
         }
     }
+}
+
+// Launches the merge kernel. `after_partial`: it directly follows the partial kernel on the same stream, so it is
+// launched with programmatic stream serialisation - its blocks are set up while the partial kernel still runs and
+// wait inside the kernel (griddepcontrol.wait) until that grid has completed.
+template <typename T, bool kTriples>
+void LaunchMerge(unsigned blocks, cudaStream_t stream, bool after_partial, const MergeSource& src, int64_t rows, int parts,
+                 int head_dim, void* out, int64_t heads, int64_t o_sb, int64_t o_sh) {
+    cudaLaunchConfig_t cfg{};
+    cfg.gridDim = dim3(blocks);
+    cfg.blockDim = dim3(256);
+    cfg.dynamicSmemBytes = 0;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr{};
+    attr.id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr.val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = &attr;
+    cfg.numAttrs = after_partial ? 1 : 0;
+    cudaLaunchKernelEx(&cfg, decode_merge_kernel<T, kTriples>, src, rows, parts, head_dim, out, heads, o_sb, o_sh);
 }
 
 template <typename T, int D, bool kPaged, bool kHi>
@@ -642,16 +683,13 @@ int LaunchMergeOut(const ScaDecodeFwdParams& p, cudaStream_t stream) {
     const int hd = static_cast<int>(p.head_dim);
     switch (p.dtype) {
         case SCA_DTYPE_F16:
-            decode_merge_kernel<__half, false><<<blocks, 256, 0, stream>>>(
-                src, rows, parts, hd, p.out, p.num_heads, p.o_stride.s_b, p.o_stride.s_h);
+            LaunchMerge<__half, false>(blocks, stream, true, src, rows, parts, hd, p.out, p.num_heads, p.o_stride.s_b, p.o_stride.s_h);
             break;
         case SCA_DTYPE_BF16:
-            decode_merge_kernel<__nv_bfloat16, false><<<blocks, 256, 0, stream>>>(
-                src, rows, parts, hd, p.out, p.num_heads, p.o_stride.s_b, p.o_stride.s_h);
+            LaunchMerge<__nv_bfloat16, false>(blocks, stream, true, src, rows, parts, hd, p.out, p.num_heads, p.o_stride.s_b, p.o_stride.s_h);
             break;
         default:
-            decode_merge_kernel<float, false><<<blocks, 256, 0, stream>>>(
-                src, rows, parts, hd, p.out, p.num_heads, p.o_stride.s_b, p.o_stride.s_h);
+            LaunchMerge<float, false>(blocks, stream, true, src, rows, parts, hd, p.out, p.num_heads, p.o_stride.s_b, p.o_stride.s_h);
             break;
     }
     return CheckLaunch("decode_merge_kernel", stream);
@@ -788,8 +826,7 @@ extern "C" int sca_launch_decode_triples(const ScaDecodeFwdParams* params, float
     src.o_part_stride = p.head_dim;
     const int64_t rows = p.batch * p.num_heads;
     const unsigned blocks = static_cast<unsigned>(std::min<int64_t>((rows * p.head_dim + 255) / 256, 1 << 20));
-    decode_merge_kernel<float, true><<<blocks, 256, 0, s>>>(src, rows, static_cast<int>(p.num_splits),
-                                                           static_cast<int>(p.head_dim), triples, 1, 0, 0);
+    LaunchMerge<float, true>(blocks, s, true, src, rows, static_cast<int>(p.num_splits), static_cast<int>(p.head_dim), triples, 1, 0, 0);
     return CheckLaunch("decode_merge_kernel(triples)", s);
 }
 
@@ -815,13 +852,13 @@ extern "C" int sca_launch_merge_triples(const float* gathered, int64_t ranks, in
     // rows are written densely: [rows, head_dim]
     switch (out_dtype) {
         case SCA_DTYPE_F16:
-            decode_merge_kernel<__half, false><<<blocks, 256, 0, s>>>(src, rows, parts, hd, out, 1, head_dim, 0);
+            LaunchMerge<__half, false>(blocks, s, false, src, rows, parts, hd, out, 1, head_dim, 0);
             break;
         case SCA_DTYPE_BF16:
-            decode_merge_kernel<__nv_bfloat16, false><<<blocks, 256, 0, s>>>(src, rows, parts, hd, out, 1, head_dim, 0);
+            LaunchMerge<__nv_bfloat16, false>(blocks, s, false, src, rows, parts, hd, out, 1, head_dim, 0);
             break;
         case SCA_DTYPE_F32:
-            decode_merge_kernel<float, false><<<blocks, 256, 0, s>>>(src, rows, parts, hd, out, 1, head_dim, 0);
+            LaunchMerge<float, false>(blocks, s, false, src, rows, parts, hd, out, 1, head_dim, 0);
             break;
         default: return Fail(SCA_INVALID_ARGUMENT, "merge triples: unsupported dtype id");
     }

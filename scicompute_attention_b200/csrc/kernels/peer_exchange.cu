@@ -67,6 +67,9 @@ seqsplit_exchange_kernel(const ExchangeParams p) {
     unsigned char* local = p.peer[p.rank];
     __shared__ int s_ok;
     __shared__ unsigned s_epoch;
+    // launched with programmatic stream serialisation behind the split-K partial kernel: blocks may be resident
+    // early; nothing is read before that grid has completed (a no-op after an ordinary launch)
+    asm volatile("griddepcontrol.wait;\n" ::: "memory");
     // The epoch is either given by the host or counted in the buffer header, which makes the launch parameters
     // identical from step to step (a captured graph can then replay the step). Every CTA reads the count before it
     // counts itself in `arrived`; the last CTA to arrive advances it, so no CTA can see the new value too early.
@@ -277,10 +280,19 @@ extern "C" int sca_launch_seqsplit_exchange(const ScaSeqSplitExchange* params, v
     cudaStream_t s = static_cast<cudaStream_t>(stream);
     // co-resident by construction: at most two 128-thread CTAs per SM
     const unsigned grid = static_cast<unsigned>(std::min<int64_t>(x.rows, 2LL * SmCount()));
+    cudaLaunchConfig_t cfg{};
+    cfg.gridDim = dim3(grid);
+    cfg.blockDim = dim3(128);
+    cfg.stream = s;
+    cudaLaunchAttribute attr{};
+    attr.id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr.val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = &attr;
+    cfg.numAttrs = 1;
     switch (x.out_dtype) {
-        case SCA_DTYPE_F16: seqsplit_exchange_kernel<__half><<<grid, 128, 0, s>>>(p); break;
-        case SCA_DTYPE_BF16: seqsplit_exchange_kernel<__nv_bfloat16><<<grid, 128, 0, s>>>(p); break;
-        case SCA_DTYPE_F32: seqsplit_exchange_kernel<float><<<grid, 128, 0, s>>>(p); break;
+        case SCA_DTYPE_F16: cudaLaunchKernelEx(&cfg, seqsplit_exchange_kernel<__half>, p); break;
+        case SCA_DTYPE_BF16: cudaLaunchKernelEx(&cfg, seqsplit_exchange_kernel<__nv_bfloat16>, p); break;
+        case SCA_DTYPE_F32: cudaLaunchKernelEx(&cfg, seqsplit_exchange_kernel<float>, p); break;
         default: return Fail(SCA_INVALID_ARGUMENT, "sequence-split exchange: unsupported dtype id");
     }
     return CheckLaunch("seqsplit_exchange_kernel", s);
