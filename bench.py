@@ -1,29 +1,35 @@
 #!/usr/bin/env python
 """Benchmark of the attention hot path on B200: one JSON line on stdout.
 
-  python bench.py [--gpus N] [--steps K] [--warmup W] [--workload flash|decode|paged]
-  python bench.py --impl reference ...      # the reference's CPU path on the host cores
+  python bench.py [--gpus N] [--steps K] [--warmup W]      # headline + every other workload ("secondary")
+  python bench.py --workload decode|paged|longctx|flash|kvfill ...   # that workload alone (profiling)
+  python bench.py --impl reference ...                      # the reference's CPU path on the host cores
 
-A "step" is one pass of the hot path over one batch of seeded synthetic input that is already
-resident in HBM. Timed with CUDA events on the launching stream between barrier + synchronize on
-both sides; with N > 1 ranks (one process per GPU) every rank runs the same per-GPU workload on its
-own independent sequences (no data-path collective), the slowest rank's time is taken and the
-reported value is the work of all ranks divided by it ("weak" scaling).
+A "step" is one pass of the hot path over one batch of seeded synthetic input that is already resident in
+HBM. A measurement is `repeats` blocks of K steps; every block is bracketed by barrier + synchronize on both
+sides and timed with CUDA events on the launching stream; with N > 1 ranks (one process per GPU, torchrun)
+the slowest rank's time counts for every block; `value` is the median block, min and max are reported beside it.
 
-Workloads (shapes of a Qwen3-4B attention layer: H_q = 32, H_kv = 8, D = 128):
-  flash   causal prefill, B = 4, S = 4096, bf16      -> TFLOP/s, FLOPs = 4 B H_q D S (S + 1) / 2
-  decode  split-K decode, B = 128, S_kv = 4096, bf16  -> GB/s over bytes(K) + bytes(V) + bytes(Q) + bytes(O)
-  paged   256 sequences, lengths U[512, 8192], 16-token pages in a 160k-block pool with a shuffled
-          free list; one token appended per sequence, then attended -> GB/s over the KV bytes read
-  longctx B = 8, S_kv = 131072 with the KV sequence split over the ranks (strong scaling); the partial
-          (m, l, O) triples cross NVLink inside one merge kernel over peer-mapped buffers
-          (--exchange nccl: one NCCL all-gather between two kernels) -> GB/s over the whole K/V
+The top-level line is the headline: causal flash prefill of the Qwen3-4B layer shape, every GPU on its own
+independent batch ("weak"). `secondary` carries the rest of the metric, each entry with its own roofline,
+clocks and end-to-end number:
+  flash    the same prefill in fp16 and at head dims 64 / 256                      -> TFLOP/s
+  decode   split-K decode, B = 128, S_kv = 4096, bf16                               -> GB/s over K, V, Q, O
+  paged    256 sequences, lengths U[512, 8192], 16-token pages, 160k-block pool with a shuffled free
+           list; one token appended per sequence, then attended                     -> GB/s over the KV read
+  longctx  B = 8, S_kv = 131072 (and D = 64 / 256 at 32768) with the KV SEQUENCE split over the ranks
+           ("strong"); the (m, l, O) triples cross NVLink inside one kernel over peer-mapped buffers, and
+           through one NCCL all-gather for comparison                               -> GB/s over the whole K/V
+  kvfill   prefill-sized append, block reset and block gather of the KV pool        -> GB/s
+At N > 1 the batched configurations are ALSO run divided over the ranks as the layer shape shards naturally -
+(batch x kv head) units for prefill, sequences for decode / paged decode, rank g of G owning units g, g + G, ... -
+and reported as "<name>_strong" entries with "scaling": "strong" (total work fixed, no data-path collective).
 """
 from __future__ import annotations
 
 import argparse
+import gc
 import json
-import math
 import os
 import sys
 import threading
@@ -104,57 +110,206 @@ class ClockSampler:
 # workloads
 # --------------------------------------------------------------------------------------------------
 class Workload:
+    """setup() builds this rank's device tensors, step() runs the hot path once, work_per_step() is the algorithmic
+    work of the WHOLE job per step when scaling == "strong" and of one rank otherwise."""
     name = ""
     metric = ""
     unit = ""
     bound = ""
+    scaling = "weak"
+    dtype_name = "bf16"
     launches_per_step = 0
+    default_steps = 20
+    traffic_bytes = None
+    has_e2e = True
+    h2d = d2h = 0
 
-    def setup(self, torch, device, seed): ...
+    def setup(self, torch, device, seed, rank, world): ...
     def step(self): ...
-    def work_per_step(self): ...          # algorithmic bytes or flops of one step
+    def work_per_step(self): ...
+    def config(self): ...
     def e2e_setup(self, torch): ...
-    def e2e_step(self): ...               # H2D + step + D2H; returns nothing
-    def cpu_sample(self, threads, impl): ...  # -> (work_done, seconds, description, kind)
+    def e2e_step(self): ...
+    def cpu_sample(self, threads, impl): return None
+    def teardown(self): ...
 
     def traffic(self):
-        return getattr(self, "traffic_bytes", None)
+        return self.traffic_bytes
 
 
-class DecodeWorkload(Workload):
-    name = "splitk_decode_B128_Skv4096_Hq32_Hkv8_D128_bf16"
-    metric, unit, bound = "decode_kv_bandwidth", "GB/s", "hbm"
-    launches_per_step = 2  # partial + merge
-    B, SKV = 128, 4096
-    # dram__bytes_read + dram__bytes_write of decode_partial_kernel, ncu capture at B=16 scaled x8
-    # (profiles/decode_splitk_c3.md); traffic grows in proportion to the batch
-    traffic_bytes = (268.61e6 + 5.8e6) * 8
+L2_BYTES = 126e6
 
-    def setup(self, torch, device, seed):
+
+def replicas_for(bytes_per_step):
+    """How many copies of a step's inputs to rotate through so that consecutive steps never find their data in L2:
+    1 when one step already moves more than twice the L2, otherwise enough copies to cover 400 MB."""
+    if bytes_per_step >= 2 * L2_BYTES:
+        return 1
+    return int(-(-400e6 // max(bytes_per_step, 1.0)))
+
+
+def _units(n, rank, world, strong):
+    from scicompute_attention_b200 import multi_gpu
+    return multi_gpu.units_for_rank(n, rank, world) if strong else list(range(n))
+
+
+class FlashWorkload(Workload):
+    metric, unit, bound = "flash_prefill_throughput", "TFLOP/s", "tensor"
+    launches_per_step = 1
+    default_steps = 20
+
+    def __init__(self, dtype_name="bf16", head_dim=128, strong=False, batch=4, seq=4096):
+        self.dtype_name, self.d, self.strong, self.B, self.S = dtype_name, head_dim, strong, batch, seq
+        self.scaling = "strong" if strong else "weak"
+        self.name = f"flash_prefill_causal_B{batch}_S{seq}_Hq{HQ}_Hkv{HKV}_D{head_dim}_{dtype_name}" + ("_strong" if strong else "")
+        # dram__bytes_read + dram__bytes_write of flash_fwd_sm100_kernel, ncu capture at B=1 scaled x4
+        # (profiles/flash_prefill_c2.md); the output mostly stays in L2 until after the kernel
+        self.traffic_bytes = (50.41e6 + 2.9e6) * batch if (head_dim == 128 and not strong) else None
+
+    def setup(self, torch, device, seed, rank, world):
         from scicompute_attention_b200 import ops
         self.torch, self.ops = torch, ops
         g = torch.Generator(device=device).manual_seed(seed)
-        self.q = torch.randn((self.B, HQ, 1, D), generator=g, device=device, dtype=torch.float32).to(torch.bfloat16)
-        self.k = torch.randn((self.B, HKV, self.SKV, D), generator=g, device=device, dtype=torch.bfloat16)
-        self.v = torch.randn((self.B, HKV, self.SKV, D), generator=g, device=device, dtype=torch.bfloat16)
-        self.out = None
+        dt = torch.float16 if self.dtype_name == "fp16" else torch.bfloat16
+        # independent units of a GQA prefill: (batch, kv head) with the `group` query heads that read it; the strong
+        # variant deals them round-robin to the ranks and runs a rank's share as one batch of single-kv-head problems
+        units = _units(self.B * HKV, rank, world, self.strong)
+        self.world = world
+        self.group = HQ // HKV
+        if self.strong:
+            self.shape_q, self.shape_kv = (len(units), self.group, self.S, self.d), (len(units), 1, self.S, self.d)
+        else:
+            self.shape_q, self.shape_kv = (self.B, HQ, self.S, self.d), (self.B, HKV, self.S, self.d)
+        nq, nkv = 1, 1
+        for n in self.shape_q:
+            nq *= n
+        for n in self.shape_kv:
+            nkv *= n
+        self.sets = []
+        for _ in range(replicas_for((2 * nq + 2 * nkv) * 2)):  # a rank's share may fit into L2: rotate copies
+            q = torch.randn(self.shape_q, generator=g, device=device, dtype=torch.float32).to(dt)
+            k = torch.randn(self.shape_kv, generator=g, device=device, dtype=torch.float32).to(dt)
+            v = torch.randn(self.shape_kv, generator=g, device=device, dtype=torch.float32).to(dt)
+            self.sets.append((q, k, v, torch.empty_like(q)))
+        self.q, self.k, self.v, self.out = self.sets[0]
+        self.turn = 0
 
     def step(self):
-        self.out = self.ops.decode_attention(self.q, self.k, self.v)
+        q, k, v, out = self.sets[self.turn]
+        self.turn = (self.turn + 1) % len(self.sets)
+        if q.shape[0] > 0:
+            self.ops.flash_attention(q, k, v, causal=True, out=out)
 
     def work_per_step(self):
-        return 2 * self.B * HKV * self.SKV * D * 2 + 2 * self.B * HQ * D * 2
+        return 4 * self.B * HQ * self.d * (self.S * (self.S + 1) // 2)
 
     def config(self):
-        return {"workload": self.name, "batch": self.B, "seq_kv": self.SKV, "heads_q": HQ, "heads_kv": HKV,
-                "head_dim": D, "l2_policy": "inputs larger than L2 (2.1 GB per step)",
-                "sharding": "independent sequences per GPU, no collective"}
+        copies = len(getattr(self, "sets", [None]))
+        moved = (2 * self.B * HQ + 2 * self.B * HKV) * self.S * self.d * 2 / (getattr(self, "world", 1) if self.strong else 1)
+        return {"workload": self.name, "batch": self.B, "seq_len": self.S, "heads_q": HQ, "heads_kv": HKV,
+                "head_dim": self.d, "causal": True,
+                "l2_policy": ("%d copies of a rank's share (%.0f MB each) used in rotation: larger than L2 together" % (copies, moved / 1e6))
+                if copies > 1 else "inputs + output (%.0f MB per GPU and step) larger than L2" % (moved / 1e6),
+                "sharding": "(batch, kv head) units dealt round-robin to the ranks, no collective" if self.strong
+                else "every GPU runs the whole configuration on its own inputs, no collective"}
 
     def e2e_setup(self, torch):
         self.hq = self.q.cpu().pin_memory()
         self.hk = self.k.cpu().pin_memory()
         self.hv = self.v.cpu().pin_memory()
-        self.ho = torch.empty((self.B, HQ, 1, D), dtype=torch.bfloat16).pin_memory()
+        self.ho = torch.empty(self.q.shape, dtype=self.q.dtype).pin_memory()
+        self.h2d = (self.hq.numel() + self.hk.numel() + self.hv.numel()) * 2
+        self.d2h = self.ho.numel() * 2
+        self.e2e_streams = [torch.cuda.Stream() for _ in range(self.q.shape[0])]
+
+    def e2e_step(self):
+        # one stream per batch element: the upload of prompt b + 1 overlaps the kernel and the download of prompt b
+        # (the two copy directions are separate engines); the launching stream joins all of them at the end, so the
+        # events around the timed region see the whole step
+        torch = self.torch
+        cur = torch.cuda.current_stream()
+        for b in range(self.q.shape[0]):
+            side = self.e2e_streams[b]
+            side.wait_stream(cur)
+            with torch.cuda.stream(side):
+                self.q[b:b + 1].copy_(self.hq[b:b + 1], non_blocking=True)
+                self.k[b:b + 1].copy_(self.hk[b:b + 1], non_blocking=True)
+                self.v[b:b + 1].copy_(self.hv[b:b + 1], non_blocking=True)
+                self.ops.flash_attention(self.q[b:b + 1], self.k[b:b + 1], self.v[b:b + 1], causal=True,
+                                         out=self.out[b:b + 1], stream=side)
+                self.ho[b:b + 1].copy_(self.out[b:b + 1], non_blocking=True)
+        for side in self.e2e_streams:
+            cur.wait_stream(side)
+
+    def cpu_sample(self, threads, impl):
+        # bounded sample: one (batch 0, head) pair per host thread; the main arm's CPU leg takes whole
+        # causal heads (all rows), one step of the reference arm the last 256 query rows (row i attends to
+        # i + 1 keys); FLOPs are counted for the sampled rows only
+        import numpy as np
+        skv = self.q.shape[2]
+        sq = skv if impl == "port" else min(256, skv)
+        hq_have, hkv_have = self.q.shape[1], self.k.shape[1]
+        nh = max(1, min(hq_have, threads))
+        q = self.q[:1, :nh, skv - sq:skv].float().cpu().numpy()
+        k = self.k[:1, :, :skv].float().cpu().numpy()
+        v = self.v[:1, :, :skv].float().cpu().numpy()
+        k = np.repeat(k, hq_have // hkv_have, axis=1)[:, :nh]
+        v = np.repeat(v, hq_have // hkv_have, axis=1)[:, :nh]
+        secs, kind = run_cpu_attention(q, np.ascontiguousarray(k), np.ascontiguousarray(v), True, threads, impl)
+        flops = 4 * nh * self.d * sum(skv - sq + i + 1 for i in range(sq))
+        return flops, secs, f"{nh} heads x last {sq} query rows of a {skv}-token causal prefix", kind
+
+
+class DecodeWorkload(Workload):
+    metric, unit, bound = "decode_kv_bandwidth", "GB/s", "hbm"
+    launches_per_step = 2  # partial + merge
+    default_steps = 50
+
+    def __init__(self, strong=False, batch=128, seq=4096):
+        self.strong, self.B, self.SKV = strong, batch, seq
+        self.scaling = "strong" if strong else "weak"
+        self.name = f"splitk_decode_B{batch}_Skv{seq}_Hq{HQ}_Hkv{HKV}_D{D}_bf16" + ("_strong" if strong else "")
+        # dram__bytes_read + dram__bytes_write of decode_partial_kernel, ncu capture at B=16 scaled by the batch
+        # (profiles/decode_splitk_c3.md); traffic grows in proportion to the batch
+        self.traffic_bytes = (268.61e6 + 5.8e6) * batch / 16 if not strong else None
+
+    def setup(self, torch, device, seed, rank, world):
+        from scicompute_attention_b200 import ops
+        self.torch, self.ops = torch, ops
+        nb = len(_units(self.B, rank, world, self.strong))
+        g = torch.Generator(device=device).manual_seed(seed)
+        self.sets = []
+        for _ in range(replicas_for(2 * nb * HKV * self.SKV * D * 2)):
+            q = torch.randn((nb, HQ, 1, D), generator=g, device=device, dtype=torch.float32).to(torch.bfloat16)
+            k = torch.randn((nb, HKV, self.SKV, D), generator=g, device=device, dtype=torch.bfloat16)
+            v = torch.randn((nb, HKV, self.SKV, D), generator=g, device=device, dtype=torch.bfloat16)
+            self.sets.append((q, k, v))
+        self.q, self.k, self.v = self.sets[0]
+        self.turn = 0
+        self.out = None
+
+    def step(self):
+        q, k, v = self.sets[self.turn]
+        self.turn = (self.turn + 1) % len(self.sets)
+        if q.shape[0] > 0:
+            self.out = self.ops.decode_attention(q, k, v)
+
+    def work_per_step(self):
+        return 2 * self.B * HKV * self.SKV * D * 2 + 2 * self.B * HQ * D * 2
+
+    def config(self):
+        mine = 2 * self.k.numel() * 2
+        copies = len(getattr(self, "sets", [None]))
+        return {"workload": self.name, "batch": self.B, "seq_kv": self.SKV, "heads_q": HQ, "heads_kv": HKV,
+                "head_dim": D, "l2_policy": "inputs larger than L2 (%d x %.0f MB per GPU, used in rotation)" % (copies, mine / 1e6),
+                "sharding": "sequences dealt round-robin to the ranks, no collective" if self.strong
+                else "every GPU runs the whole batch on its own sequences, no collective"}
+
+    def e2e_setup(self, torch):
+        self.hq = self.q.cpu().pin_memory()
+        self.hk = self.k.cpu().pin_memory()
+        self.hv = self.v.cpu().pin_memory()
+        self.ho = torch.empty((self.q.shape[0], HQ, 1, D), dtype=torch.bfloat16).pin_memory()
         self.h2d = self.hq.numel() * 2 + self.hk.numel() * 2 + self.hv.numel() * 2
         self.d2h = self.ho.numel() * 2
 
@@ -166,7 +321,6 @@ class DecodeWorkload(Workload):
         self.ho.copy_(out, non_blocking=True)
 
     def cpu_sample(self, threads, impl):
-        import numpy as np
         # CPU leg of the main arm: the whole batch (a second or two of FP64 work on all host threads);
         # one step of the reference arm: eight sequences per host thread of the reference's own routine
         nb = self.q.shape[0] if impl == "port" else max(1, min(self.q.shape[0], 8 * threads))
@@ -179,30 +333,42 @@ class DecodeWorkload(Workload):
 
 
 class PagedWorkload(Workload):
-    name = "paged_decode_256seq_len512-8192_bs16_pool160k_Hq32_Hkv8_D128_bf16"
     metric, unit, bound = "paged_decode_kv_bandwidth", "GB/s", "hbm"
     launches_per_step = 3  # batched append + partial + merge
-    NSEQ, BS, NBLK = 256, 16, 160000
+    default_steps = 30
     # ncu capture of the paged decode_partial_kernel on 32 sequences: 606.3 MB moved for 597.7 MB of K/V
-    # (profiles/paged_decode_c4.md); scaled by the tokens of the full batch in roofline()
+    # (profiles/paged_decode_c4.md); scaled by the tokens of the full batch
     traffic_ratio = (598.10e6 + 8.21e6) / 597.75e6
 
-    def setup(self, torch, device, seed):
+    def __init__(self, strong=False, nseq=256, nblk=160000):
+        self.strong, self.NSEQ, self.NBLK, self.BS = strong, nseq, nblk, 16
+        self.scaling = "strong" if strong else "weak"
+        self.name = (f"paged_decode_{nseq}seq_len512-8192_bs16_pool{nblk // 1000}k_Hq{HQ}_Hkv{HKV}_D{D}_bf16"
+                     + ("_strong" if strong else ""))
+
+    def setup(self, torch, device, seed, rank, world):
         import numpy as np
-        sys.path.insert(0, os.path.join(ROOT, "oracle"))
         from scicompute_attention_b200 import ops
         self.torch, self.ops, self.np = torch, ops, np
-        rng = np.random.default_rng(seed)
-        self.lens = rng.integers(512, 8193, size=self.NSEQ).astype(np.int64)
+        # the whole job's lengths come from one seed; the strong variant gives rank g sequences g, g + G, ... and a
+        # pool of its own of 1/G of the blocks (every rank owns allocator, table and pool, as the sharding says)
+        rng = np.random.default_rng(seed if not self.strong else 12345)
+        all_lens = rng.integers(512, 8193, size=self.NSEQ).astype(np.int64)
+        mine = _units(self.NSEQ, rank, world, self.strong)
+        self.all_lens = all_lens
+        self.lens = all_lens[mine]
+        nseq = len(mine)
+        nblk = self.NBLK // world if self.strong else self.NBLK
+        self.nblk = nblk
         # LIFO allocator with a seeded shuffle of its free list -> non-contiguous page tables. The
         # allocation order is the reference's: allocate everything, shuffle, free in that order, then
         # every allocation pops from the back (src/kv_cache/block_manager.cpp:25-27,60-62).
-        ids = np.arange(self.NBLK, dtype=np.int32)
-        rng.shuffle(ids)
-        free = list(ids)  # freed in this order; allocation pops from the back
-        max_blocks = self.NBLK  # table row length = pool size (src/kv_cache/paged_kv_cache.cpp:22-27)
-        table = np.full((self.NSEQ, max_blocks), -1, dtype=np.int32)
-        for s in range(self.NSEQ):
+        ids = np.arange(nblk, dtype=np.int32)
+        np.random.default_rng(seed + 1).shuffle(ids)
+        free = list(ids)
+        max_blocks = nblk  # table row length = pool size (src/kv_cache/paged_kv_cache.cpp:22-27)
+        table = np.full((max(nseq, 1), max_blocks), -1, dtype=np.int32)
+        for s in range(nseq):
             need = -(-(int(self.lens[s]) + 1) // self.BS)
             for j in range(need):
                 table[s, j] = free.pop()
@@ -210,34 +376,40 @@ class PagedWorkload(Workload):
         self.page_table = torch.from_numpy(table).to(device)
         self.seq_lens = torch.from_numpy((self.lens + 1).astype(np.int32)).to(device)  # includes the new token
         g = torch.Generator(device=device).manual_seed(seed)
-        shape = (self.NBLK, self.BS, HKV, D)
+        shape = (nblk, self.BS, HKV, D)
         self.k_pool = torch.randn(shape, generator=g, device=device, dtype=torch.bfloat16)
         self.v_pool = torch.randn(shape, generator=g, device=device, dtype=torch.bfloat16)
-        self.q = torch.randn((self.NSEQ, HQ, 1, D), generator=g, device=device, dtype=torch.float32).to(torch.bfloat16)
-        self.k_new = torch.randn((self.NSEQ, HKV, D), generator=g, device=device, dtype=torch.bfloat16)
-        self.v_new = torch.randn((self.NSEQ, HKV, D), generator=g, device=device, dtype=torch.bfloat16)
-        self.mean_len = int(self.lens.mean()) + 1
-        # scheduling hint: longest sequences first (the host knows the lengths of its batch)
-        self.seq_order = torch.from_numpy(np.argsort(-self.lens, kind="stable").astype(np.int32)).to(device)
+        self.q = torch.randn((nseq, HQ, 1, D), generator=g, device=device, dtype=torch.float32).to(torch.bfloat16)
+        self.k_new = torch.randn((nseq, HKV, D), generator=g, device=device, dtype=torch.bfloat16)
+        self.v_new = torch.randn((nseq, HKV, D), generator=g, device=device, dtype=torch.bfloat16)
+        self.mean_len = int(self.lens.mean()) + 1 if nseq else 1
+        self.longest = int(self.lens.max()) + 1 if nseq else 1
 
     def step(self):
+        if self.q.shape[0] == 0:
+            return
         self.ops.kv_append_batched(self.k_pool, self.v_pool, self.k_new, self.v_new, self.page_table, self.seq_lens)
         self.out = self.ops.paged_attention(self.q, self.k_pool, self.v_pool, self.page_table, self.seq_lens,
-                                            block_size=self.BS, typical_len=self.mean_len, seq_order=self.seq_order)
+                                            block_size=self.BS, typical_len=self.mean_len, longest_len=self.longest)
+
+    def _bytes(self, lens):
+        toks = int((lens + 1).sum())
+        pages = int(sum(-(-(int(n) + 1) // self.BS) for n in lens))
+        return toks * (2 * HKV * D * 2) + 2 * len(lens) * HQ * D * 2 + pages * 4 + len(lens) * 4
 
     def work_per_step(self):
-        toks = int((self.lens + 1).sum())
-        pages = int(sum(-(-(int(n) + 1) // self.BS) for n in self.lens))
-        return toks * (2 * HKV * D * 2) + 2 * self.NSEQ * HQ * D * 2 + pages * 4 + self.NSEQ * 4
+        return self._bytes(self.all_lens if self.strong else self.lens)
 
     def traffic(self):
-        return float((self.lens + 1).sum()) * 2 * HKV * D * 2 * self.traffic_ratio
+        return None if self.strong else float((self.lens + 1).sum()) * 2 * HKV * D * 2 * self.traffic_ratio
 
     def config(self):
         return {"workload": self.name, "num_seqs": self.NSEQ, "block_size": self.BS, "pool_blocks": self.NBLK,
-                "tokens_attended": int((self.lens + 1).sum()), "heads_q": HQ, "heads_kv": HKV, "head_dim": D,
-                "l2_policy": "inputs larger than L2 (4.6 GB of KV read per step)",
-                "sharding": "independent sequences and pools per GPU, no collective"}
+                "tokens_attended": int(((self.all_lens if self.strong else self.lens) + 1).sum()), "heads_q": HQ,
+                "heads_kv": HKV, "head_dim": D,
+                "l2_policy": "inputs larger than L2 (%.0f MB of KV read per GPU and step)" % (float((self.lens + 1).sum()) * 4096 / 1e6),
+                "sharding": "sequences dealt round-robin to the ranks, every rank with its own pool and page table, no collective"
+                if self.strong else "every GPU runs the whole batch on its own pool, no collective"}
 
     def e2e_setup(self, torch):
         # what a serving loop moves per step: the new tokens' q/k/v up, the attention output down;
@@ -245,7 +417,7 @@ class PagedWorkload(Workload):
         self.hq = self.q.cpu().pin_memory()
         self.hkn = self.k_new.cpu().pin_memory()
         self.hvn = self.v_new.cpu().pin_memory()
-        self.ho = torch.empty((self.NSEQ, HQ, 1, D), dtype=torch.bfloat16).pin_memory()
+        self.ho = torch.empty((self.q.shape[0], HQ, 1, D), dtype=torch.bfloat16).pin_memory()
         self.h2d = (self.hq.numel() + self.hkn.numel() + self.hvn.numel()) * 2
         self.d2h = self.ho.numel() * 2
 
@@ -280,160 +452,195 @@ class PagedWorkload(Workload):
         return work, secs, f"{ns} of {self.NSEQ} sequences (gathered to contiguous K/V), all heads", kind
 
 
-class FlashWorkload(Workload):
-    name = "flash_prefill_causal_B4_S4096_Hq32_Hkv8_D128_bf16"
-    metric, unit, bound = "flash_prefill_throughput", "TFLOP/s", "tensor"
-    launches_per_step = 1
-    B, S = 4, 4096
-    # dram__bytes_read + dram__bytes_write of flash_fwd_sm100_kernel, ncu capture at B=1 scaled x4
-    # (profiles/flash_prefill_c2.md); the output mostly stays in L2 until after the kernel
-    traffic_bytes = (50.41e6 + 2.9e6) * 4
-    dtype_name = "bf16"  # --dtype fp16 runs the same configuration in half precision
-
-    def setup(self, torch, device, seed):
-        from scicompute_attention_b200 import ops
-        self.torch, self.ops = torch, ops
-        g = torch.Generator(device=device).manual_seed(seed)
-        dt = torch.float16 if self.dtype_name == "fp16" else torch.bfloat16
-        self.q = torch.randn((self.B, HQ, self.S, D), generator=g, device=device, dtype=torch.float32).to(dt)
-        self.k = torch.randn((self.B, HKV, self.S, D), generator=g, device=device, dtype=torch.float32).to(dt)
-        self.v = torch.randn((self.B, HKV, self.S, D), generator=g, device=device, dtype=torch.float32).to(dt)
-        self.out = torch.empty_like(self.q)
-        # 256 MiB scratch written between steps would flush L2; inputs + output (320 MiB) already exceed it
-        self.flush = None
-
-    def step(self):
-        self.ops.flash_attention(self.q, self.k, self.v, causal=True, out=self.out)
-
-    def work_per_step(self):
-        return 4 * self.B * HQ * D * (self.S * (self.S + 1) // 2)
-
-    def config(self):
-        return {"workload": self.name.replace("bf16", self.dtype_name), "batch": self.B, "seq_len": self.S, "heads_q": HQ,
-                "heads_kv": HKV, "head_dim": D, "causal": True,
-                "l2_policy": "inputs + output (335 MB per step) larger than L2",
-                "sharding": "independent (batch, kv-head group) units per GPU, no collective"}
-
-    def e2e_setup(self, torch):
-        self.hq = self.q.cpu().pin_memory()
-        self.hk = self.k.cpu().pin_memory()
-        self.hv = self.v.cpu().pin_memory()
-        self.ho = torch.empty(self.q.shape, dtype=self.q.dtype).pin_memory()
-        self.h2d = (self.hq.numel() + self.hk.numel() + self.hv.numel()) * 2
-        self.d2h = self.ho.numel() * 2
-        self.e2e_streams = [torch.cuda.Stream() for _ in range(self.B)]
-
-    def e2e_step(self):
-        # one stream per batch element: the upload of prompt b + 1 overlaps the kernel and the download of prompt b
-        # (the two copy directions are separate engines); the launching stream joins all of them at the end, so the
-        # events around the timed region see the whole step
-        torch = self.torch
-        cur = torch.cuda.current_stream()
-        for b in range(self.B):
-            side = self.e2e_streams[b]
-            side.wait_stream(cur)
-            with torch.cuda.stream(side):
-                self.q[b:b + 1].copy_(self.hq[b:b + 1], non_blocking=True)
-                self.k[b:b + 1].copy_(self.hk[b:b + 1], non_blocking=True)
-                self.v[b:b + 1].copy_(self.hv[b:b + 1], non_blocking=True)
-                self.ops.flash_attention(self.q[b:b + 1], self.k[b:b + 1], self.v[b:b + 1], causal=True,
-                                         out=self.out[b:b + 1], stream=side)
-                self.ho[b:b + 1].copy_(self.out[b:b + 1], non_blocking=True)
-        for side in self.e2e_streams:
-            cur.wait_stream(side)
-
-    def cpu_sample(self, threads, impl):
-        # bounded sample: one (batch 0, head) pair per host thread; the main arm's CPU leg takes whole
-        # causal heads (all 4096 rows), one step of the reference arm the last 256 query rows (rows i attend to
-        # i + 1 keys); FLOPs are counted for the sampled rows only
-        import numpy as np
-        skv = self.q.shape[2]
-        sq = skv if impl == "port" else min(256, skv)
-        nh = max(1, min(HQ, threads))
-        q = self.q[:1, :nh, skv - sq:skv].float().cpu().numpy()
-        k = self.k[:1, :HKV, :skv].float().cpu().numpy()
-        v = self.v[:1, :HKV, :skv].float().cpu().numpy()
-        k = np.repeat(k, HQ // HKV, axis=1)[:, :nh]
-        v = np.repeat(v, HQ // HKV, axis=1)[:, :nh]
-        secs, kind = run_cpu_attention(q, np.ascontiguousarray(k), np.ascontiguousarray(v), True, threads, impl)
-        flops = 4 * nh * D * sum(skv - sq + i + 1 for i in range(sq))
-        return flops, secs, f"{nh} heads x last {sq} query rows of a {skv}-token causal prefix", kind
-
-
 class LongContextWorkload(Workload):
-    """Sequence-split decode: B = 8, S_kv = 131072; the KV axis is cut into one contiguous slice per rank,
-    every rank reduces its slice to (m, l, O) triples, B*H_q*(2+D) floats per rank travel to every peer
-    (stored by the merge kernel into peer-mapped buffers, or by one NCCL all-gather), and every rank merges.
-    Total work is fixed, so this workload scales "strong"."""
-    name = "seqsplit_decode_B8_Skv131072_Hq32_Hkv8_D128_bf16"
+    """Sequence-split decode: the KV axis is cut into one contiguous slice per rank, every rank reduces its slice to
+    (m, l, O) triples, B*H_q*(2+D) floats per rank travel to every peer (stored by the merge kernel into peer-mapped
+    buffers, or by one NCCL all-gather), and every rank merges. Total work is fixed: this workload scales "strong"."""
     metric, unit, bound = "longctx_decode_kv_bandwidth", "GB/s", "hbm"
-    launches_per_step = 2  # partial kernel + fused merge / exchange / merge (3 plus the all-gather with --exchange nccl)
     scaling = "strong"
-    B, SKV = 8, 131072
-    traffic_bytes = None
-    exchange = "peer"
+    default_steps = 300
+    B = 8
 
-    def setup(self, torch, device, seed):
-        import torch.distributed as dist
+    def __init__(self, head_dim=128, seq=131072, exchange="peer"):
+        self.d, self.SKV, self.exchange = head_dim, seq, exchange
+        self.name = f"seqsplit_decode_B8_Skv{seq}_Hq{HQ}_Hkv{HKV}_D{head_dim}_bf16"
+
+    def setup(self, torch, device, seed, rank, world):
         from scicompute_attention_b200 import multi_gpu, ops
         self.torch, self.ops, self.mg = torch, ops, multi_gpu
-        self.rank = dist.get_rank() if dist.is_initialized() else 0
-        self.world = dist.get_world_size() if dist.is_initialized() else 1
-        lo, hi = multi_gpu.kv_range_for_rank(self.SKV, self.rank, self.world)
+        self.rank, self.world = rank, world
+        if world > 1:
+            self.name += "_" + self.exchange
+        lo, hi = multi_gpu.kv_range_for_rank(self.SKV, rank, world)
         g = torch.Generator(device=device).manual_seed(1234)  # q is replicated: same seed on every rank
-        self.q = torch.randn((self.B, HQ, 1, D), generator=g, device=device, dtype=torch.float32).to(torch.bfloat16)
+        self.q = torch.randn((self.B, HQ, 1, self.d), generator=g, device=device, dtype=torch.float32).to(torch.bfloat16)
         g2 = torch.Generator(device=device).manual_seed(seed + 77)
-        self.k = torch.randn((self.B, HKV, hi - lo, D), generator=g2, device=device, dtype=torch.bfloat16)
-        self.v = torch.randn((self.B, HKV, hi - lo, D), generator=g2, device=device, dtype=torch.bfloat16)
+        self.sets = []
+        for _ in range(replicas_for(2 * self.B * HKV * (hi - lo) * self.d * 2)):  # a small share would sit in L2
+            k = torch.randn((self.B, HKV, hi - lo, self.d), generator=g2, device=device, dtype=torch.bfloat16)
+            v = torch.randn((self.B, HKV, hi - lo, self.d), generator=g2, device=device, dtype=torch.bfloat16)
+            self.sets.append((k, v))
+        self.k, self.v = self.sets[0]
+        self.turn = 0
         self.px = None
-        if self.world > 1 and self.exchange == "peer":
-            self.px = multi_gpu.PeerExchange(self.B * HQ, D, device)
-            # the whole step (partial kernel + exchange kernel) is one captured graph, replayed every step
-            self.graph, self.out = self.px.capture(self.q, self.k, self.v)
-        else:
-            self.launches_per_step = 3
+        self.launches_per_step = 2  # partial kernel + merge (1 GPU) / fused merge-exchange-merge kernel
+        if world > 1 and self.exchange == "peer":
+            self.px = multi_gpu.PeerExchange(self.B * HQ, self.d, device)
+            # the whole step (partial kernel + exchange kernel) is one captured graph per K/V copy, replayed in turn
+            self.graphs = [self.px.capture(self.q, k, v) for k, v in self.sets]
+        elif world > 1:
+            self.launches_per_step = 3  # partial, merge to triples, merge over ranks (+ the NCCL all-gather)
 
     def step(self):
+        k, v = self.sets[self.turn]
         if self.px is not None:
-            self.graph.replay()
+            graph, self.out = self.graphs[self.turn]
+            graph.replay()
+        elif self.world > 1:
+            self.out = self.mg.sequence_split_decode(self.q, k, v)
         else:
-            self.out = self.mg.sequence_split_decode(self.q, self.k, self.v)
+            self.out = self.ops.decode_attention(self.q, k, v)
+        self.turn = (self.turn + 1) % len(self.sets)
 
     def work_per_step(self):
         # whole job: all ranks together read the full K and V once
-        return 2 * self.B * HKV * self.SKV * D * 2 + 2 * self.B * HQ * D * 2
+        return 2 * self.B * HKV * self.SKV * self.d * 2 + 2 * self.B * HQ * self.d * 2
 
     def config(self):
+        mine = 2 * self.k.numel() * 2
+        copies = len(getattr(self, "sets", [None]))
         return {"workload": self.name, "batch": self.B, "seq_kv": self.SKV, "heads_q": HQ, "heads_kv": HKV,
-                "head_dim": D, "l2_policy": "inputs larger than L2 (4.3 GB over all ranks)",
+                "head_dim": self.d, "l2_policy": "inputs larger than L2 (%d x %.0f MB per GPU, used in rotation)" % (copies, mine / 1e6),
                 "sharding": "KV sequence split across ranks; (m, l, O) triples exchanged " +
-                            ("by peer stores inside the merge kernel" if self.px is not None else
+                            ("by peer stores inside the merge kernel (captured graph)" if self.px is not None else
                              "by one NCCL all-gather per step" if self.world > 1 else "locally (one rank)")}
 
     def e2e_setup(self, torch):
         self.hq = self.q.cpu().pin_memory()
-        self.ho = torch.empty((self.B * HQ, D), dtype=torch.bfloat16).pin_memory()
+        self.ho = torch.empty((self.B * HQ, self.d), dtype=torch.bfloat16).pin_memory()
         self.h2d, self.d2h = self.hq.numel() * 2, self.ho.numel() * 2
 
     def e2e_step(self):
         # a decode step moves the new query up and the attention output down; the KV cache lives on the devices
         self.q.copy_(self.hq, non_blocking=True)
         self.step()
-        self.ho.copy_(self.out, non_blocking=True)
+        self.ho.copy_(self.out.reshape(self.B * HQ, self.d), non_blocking=True)
 
     def cpu_sample(self, threads, impl):
         nb = 1
-        skv = 16384
+        skv = min(16384, self.k.shape[2])
         q = self.q[:nb].float().cpu().numpy()
         k = self.k[:nb, :, :skv].float().cpu().numpy()
         v = self.v[:nb, :, :skv].float().cpu().numpy()
         secs, kind = run_cpu_attention(q, k, v, True, threads, impl)
-        work = 2 * nb * HKV * k.shape[2] * D * 2 + 2 * nb * HQ * D * 2
+        work = 2 * nb * HKV * k.shape[2] * self.d * 2 + 2 * nb * HQ * self.d * 2
         return work, secs, f"{nb} of {self.B} sequences, first {k.shape[2]} of {self.SKV} keys, all heads", kind
 
+    def teardown(self):
+        if self.px is not None:
+            self.graphs = None
+            self.px.close()
+            self.px = None
 
-WORKLOADS = {"flash": FlashWorkload, "decode": DecodeWorkload, "paged": PagedWorkload, "longctx": LongContextWorkload}
-DEFAULT_WORKLOAD = "flash"
+
+class KvWorkload(Workload):
+    """The KV-cache data movement kernels at prefill size: `append` scatters the tokens of a ragged batch
+    (lengths U[512, 8192], 256 sequences: about 1.1 M tokens x 4096 B) into a shuffled 160k-block pool, `reset`
+    zeroes 10 000 blocks of K and V, `gather` copies 10 000 blocks into a contiguous buffer."""
+    unit, bound = "GB/s", "hbm"
+    launches_per_step = 1
+    default_steps = 10
+    has_e2e = False  # these kernels move data that lives on the device on both sides: nothing to bring from the host
+    NSEQ, NBLK, BS, NIDS = 256, 160000, 16, 10000
+
+    def __init__(self, op="append"):
+        self.op = op
+        self.metric = f"kv_{op}_bandwidth"
+        self.name = {"append": "kv_append_prefill_fill_256seq_len512-8192_bs16_pool160k",
+                     "reset": "kv_reset_10000_blocks_bs16", "gather": "kv_gather_10000_blocks_bs16"}[op] + f"_Hkv{HKV}_D{D}_bf16"
+
+    def setup(self, torch, device, seed, rank, world):
+        import numpy as np
+        from scicompute_attention_b200 import ops
+        self.torch, self.ops = torch, ops
+        rng = np.random.default_rng(seed)
+        shape = (self.NBLK, self.BS, HKV, D)
+        self.k_pool = torch.zeros(shape, device=device, dtype=torch.bfloat16)
+        self.v_pool = torch.zeros(shape, device=device, dtype=torch.bfloat16) if self.op != "gather" else None
+        perm = rng.permutation(self.NBLK).astype(np.int32)
+        if self.op == "append":
+            lens = rng.integers(512, 8193, size=self.NSEQ)
+            ntok = int(lens.sum())
+            nblocks = int(sum(-(-int(n) // self.BS) for n in lens))
+            slots = np.empty(ntok, dtype=np.int32)
+            at, blk = 0, 0
+            for n in lens:  # token t of a sequence goes to its (t // 16)-th block, blocks taken from the shuffled list
+                need = -(-int(n) // self.BS)
+                ids = perm[blk:blk + need].astype(np.int64)
+                t = np.arange(int(n))
+                slots[at:at + int(n)] = (ids[t // self.BS] * self.BS + t % self.BS).astype(np.int32)
+                at += int(n)
+                blk += need
+            assert blk == nblocks
+            self.ntok = ntok
+            self.slots = torch.from_numpy(slots).to(device)
+            g = torch.Generator(device=device).manual_seed(seed)
+            self.k_new = torch.randn((ntok, HKV, D), generator=g, device=device, dtype=torch.bfloat16)
+            self.v_new = torch.randn((ntok, HKV, D), generator=g, device=device, dtype=torch.bfloat16)
+        else:
+            self.ids = torch.from_numpy(perm[: self.NIDS].copy()).to(device)
+            self.gathered = None
+
+    def step(self):
+        if self.op == "append":
+            self.ops.kv_append(self.k_pool, self.v_pool, self.k_new, self.v_new, self.slots)
+        elif self.op == "reset":
+            self.ops.kv_reset(self.k_pool, self.v_pool, self.ids)
+        else:
+            self.gathered = self.ops.kv_gather(self.k_pool, self.ids)
+
+    def work_per_step(self):
+        block = self.BS * HKV * D * 2
+        if self.op == "append":   # K and V rows read once and written once, plus the slot list
+            return self.ntok * (HKV * D * 2) * 2 * 2 + self.ntok * 4
+        if self.op == "reset":    # K and V blocks written
+            return self.NIDS * block * 2 + self.NIDS * 4
+        return self.NIDS * block * 2 + self.NIDS * 4  # gather: one layer read + written
+
+    def config(self):
+        return {"workload": self.name, "pool_blocks": self.NBLK, "block_size": self.BS, "heads_kv": HKV, "head_dim": D,
+                "l2_policy": "working set larger than L2 (%.0f MB per step)" % (self.work_per_step() / 1e6),
+                "sharding": "every GPU on its own pool, no collective"}
+
+def build_workloads(args, world):
+    """(primary, [secondary...]) as factories, in run order."""
+    single = {
+        "flash": lambda: FlashWorkload(args.dtype),
+        "decode": lambda: DecodeWorkload(),
+        "paged": lambda: PagedWorkload(),
+        "longctx": lambda: LongContextWorkload(exchange=args.exchange),
+        "kvfill": lambda: KvWorkload("append"),
+    }
+    if args.workload != "all":
+        return single[args.workload], []
+    secondary = [
+        lambda: FlashWorkload("fp16"),
+        lambda: FlashWorkload("bf16", head_dim=64),
+        lambda: FlashWorkload("bf16", head_dim=256),
+        lambda: DecodeWorkload(),
+        lambda: PagedWorkload(),
+        lambda: LongContextWorkload(128, 131072, "peer"),
+        lambda: LongContextWorkload(64, 32768, "peer"),
+        lambda: LongContextWorkload(256, 32768, "peer"),
+        lambda: KvWorkload("append"),
+        lambda: KvWorkload("reset"),
+        lambda: KvWorkload("gather"),
+    ]
+    if world > 1:
+        secondary[5:5] = [lambda: FlashWorkload("bf16", strong=True), lambda: DecodeWorkload(strong=True),
+                          lambda: PagedWorkload(strong=True)]
+        secondary.insert(9, lambda: LongContextWorkload(128, 131072, "nccl"))
+    return single["flash"], secondary
 
 
 # --------------------------------------------------------------------------------------------------
@@ -474,21 +681,152 @@ def run_cpu_attention(q, k, v, causal, threads, impl):
 
 
 # --------------------------------------------------------------------------------------------------
+# measurement
+# --------------------------------------------------------------------------------------------------
+def _stats(values):
+    s = sorted(values)
+    return {"n": len(s), "min": s[0], "median": s[len(s) // 2], "max": s[-1]}
+
+
+def pin_to_gpu_numa_node(torch, local_rank):
+    """Pinned host buffers are placed by first touch: run this process on the CPUs of the GPU's NUMA node before it
+    allocates them. Returns the node, or None when the platform does not say."""
+    try:
+        bus = torch.cuda.get_device_properties(local_rank).pci_bus_id
+        dom = torch.cuda.get_device_properties(local_rank).pci_domain_id
+        dev = torch.cuda.get_device_properties(local_rank).pci_device_id
+        path = f"/sys/bus/pci/devices/{dom:04x}:{bus:02x}:{dev:02x}.0/numa_node"
+        node = int(open(path).read().strip())
+        if node < 0:
+            return None
+        cpus = []
+        for part in open(f"/sys/devices/system/node/node{node}/cpulist").read().strip().split(","):
+            lo, _, hi = part.partition("-")
+            cpus += list(range(int(lo), int(hi or lo) + 1))
+        allowed = sorted(set(cpus) & os.sched_getaffinity(0))
+        if allowed:
+            os.sched_setaffinity(0, allowed)
+        return node
+    except Exception:
+        return None
+
+
+def measure(wl, args, steps, repeats, ctx, with_cpu):
+    """Runs one workload: warm-up, `repeats` timed blocks of `steps` steps, the end-to-end leg, optionally the CPU leg."""
+    torch, dist, device = ctx["torch"], ctx["dist"], ctx["device"]
+    rank, world, local_rank = ctx["rank"], ctx["world"], ctx["local_rank"]
+    stream = torch.cuda.current_stream()
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    wl.setup(torch, device, args.seed + rank, rank, world)
+    for _ in range(args.warmup):
+        wl.step()
+    barrier()
+    sampler = ClockSampler(local_rank)
+    sampler.start()
+    block_ms = []
+    for _ in range(repeats):
+        start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        barrier()
+        start.record(stream)
+        for _ in range(steps):
+            wl.step()
+        stop.record(stream)
+        barrier()
+        block_ms.append(start.elapsed_time(stop))
+    clocks = sampler.stop()
+
+    # end to end through the public operator with host buffers: pinned H2D of the step's inputs,
+    # the step, D2H of its result - all inside the timed region
+    e2e_steps = args.e2e_steps or min(steps, 5)
+    e2e_ms = []
+    if not args.capture and wl.has_e2e:
+        wl.e2e_setup(torch)
+        wl.e2e_step()
+        for _ in range(3):
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            barrier()
+            e0.record(stream)
+            for _ in range(e2e_steps):
+                wl.e2e_step()
+            e1.record(stream)
+            barrier()
+            e2e_ms.append(e0.elapsed_time(e1) / e2e_steps)
+
+    if world > 1:
+        t = torch.tensor(block_ms + (e2e_ms or [0.0]), device=device, dtype=torch.float64)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        vals = [float(x) for x in t]
+        block_ms, e2e_ms = vals[:repeats], (vals[repeats:] if e2e_ms else [])
+    step_ms = _stats([ms / steps for ms in block_ms])
+    strong = wl.scaling == "strong"
+    work = wl.work_per_step()
+    scale = 1e9 if wl.unit == "GB/s" else 1e12
+    total = (1 if strong else world)
+
+    def rate(ms):
+        return work / (ms * 1e-3) / scale * total
+
+    value = rate(step_ms["median"])
+    per_gpu = value / world
+    entry = None
+    if rank == 0:
+        peaks = measured_peaks()
+        peak = peaks["hbm_gbs"] if wl.bound == "hbm" else peaks["tflops"]
+        nominal = NOMINAL_HBM_GBS if wl.bound == "hbm" else NOMINAL_TENSOR_TFLOPS
+        cpu = None
+        if with_cpu and not args.capture:
+            got = wl.cpu_sample(ctx["threads"], "port")
+            if got is not None:
+                cw, cs, desc, kind = got
+                cpu = {"value": cw / cs / scale, "unit": wl.unit, "cores": ctx["threads"], "kind": kind,
+                       "sample": desc + f" ({cs:.1f} s of FP64 host work)"}
+        e2e = None
+        if e2e_ms:
+            med = sorted(e2e_ms)[len(e2e_ms) // 2]
+            e2e = {"value": rate(med), "unit": wl.unit, "h2d_bytes_per_step": wl.h2d, "d2h_bytes_per_step": wl.d2h,
+                   "ms_per_step": med, "steps": e2e_steps, "repeats": len(e2e_ms),
+                   "host_copy_gbs_per_rank": ((wl.h2d + wl.d2h) / (med * 1e-3) / 1e9) if (wl.h2d + wl.d2h) else 0.0}
+        entry = {
+            "workload": wl.name, "metric": wl.metric, "value": value, "unit": wl.unit, "n_gpus": world, "steps": steps,
+            "warmup": args.warmup, "ms_per_step": step_ms["median"], "scaling": wl.scaling,
+            "repeats": {"n": repeats, "value_min": rate(step_ms["max"]), "value_median": value, "value_max": rate(step_ms["min"]),
+                        "ms_min": step_ms["min"], "ms_median": step_ms["median"], "ms_max": step_ms["max"]},
+            "dtype": wl.dtype_name, "config": wl.config(),
+            "roofline": {"bound": wl.bound, "achieved": per_gpu, "peak": peak, "unit": wl.unit,
+                         "frac": per_gpu / peak, "peak_source": peaks["source"],
+                         "frac_of_nominal": per_gpu / nominal, "traffic": wl.traffic(),
+                         "traffic_unit": "bytes per launch of the dominant kernel (ncu capture, scaled; see profiles/)"},
+            "cpu_baseline": cpu, "e2e": e2e,
+            "gpu_launches": wl.launches_per_step * steps * repeats,
+            "clocks": clocks,
+        }
+    barrier()
+    wl.teardown()
+    return entry
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
-    ap.add_argument("--steps", type=int, default=50)
+    ap.add_argument("--steps", type=int, default=20)
     ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--repeats", type=int, default=10, help="timed blocks of --steps steps; the median block is reported")
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
-    ap.add_argument("--workload", default=DEFAULT_WORKLOAD, choices=sorted(WORKLOADS))
+    ap.add_argument("--workload", default="all", choices=["all", "flash", "decode", "paged", "longctx", "kvfill"])
+    ap.add_argument("--no-secondary", action="store_true", help="headline only")
     ap.add_argument("--e2e-steps", type=int, default=0, help="0 = min(steps, 5)")
     ap.add_argument("--seed", type=int, default=0)
-    ap.add_argument("--dtype", default="bf16", choices=["bf16", "fp16"], help="flash workload only")
+    ap.add_argument("--dtype", default="bf16", choices=["bf16", "fp16"], help="--workload flash only")
     ap.add_argument("--exchange", default="peer", choices=["peer", "nccl"],
-                    help="longctx on more than one GPU: how the triples cross NVLink")
+                    help="--workload longctx on more than one GPU: how the triples cross NVLink")
     ap.add_argument("--capture", action="store_true",
                     help="profiler-sized variant of the workload (same kernels, a few hundred MB): flash B=1, "
-                         "decode B=16, paged 32 sequences in a 20k-block pool; skips the e2e and CPU legs")
+                         "decode B=16, paged 32 sequences in a 20k-block pool; one block, no e2e and CPU legs")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3)
 
@@ -506,95 +844,56 @@ def main():
         raise SystemExit("bench.py: no CUDA device; the B200 arm has no CPU fallback")
     torch.cuda.set_device(local_rank)
     device = torch.device("cuda", local_rank)
+    node = pin_to_gpu_numa_node(torch, local_rank)
     if world > 1:
         dist.init_process_group("nccl", device_id=device)
+    ctx = {"torch": torch, "dist": dist, "device": device, "rank": rank, "world": world, "local_rank": local_rank,
+           "threads": threads}
 
-    LongContextWorkload.exchange = args.exchange
-    FlashWorkload.dtype_name = args.dtype
-    wl = WORKLOADS[args.workload]()
+    primary_factory, secondary_factories = build_workloads(args, world)
+    primary = primary_factory()
+    repeats = 1 if args.capture else max(1, args.repeats)
     if args.capture:
-        if isinstance(wl, FlashWorkload):
-            wl.B = 1
-        elif isinstance(wl, DecodeWorkload):
-            wl.B = 16
-        else:
-            wl.NSEQ, wl.NBLK = 32, 20000
-        wl.name += "_capture"
-    wl.setup(torch, device, args.seed + rank)
-    stream = torch.cuda.current_stream()
+        if isinstance(primary, FlashWorkload):
+            primary.B = 1
+        elif isinstance(primary, DecodeWorkload):
+            primary.B = 16
+        elif isinstance(primary, PagedWorkload):
+            primary.NSEQ, primary.NBLK = 32, 20000
+        primary.name += "_capture"
+        primary.traffic_bytes = None
+    head = measure(primary, args, args.steps, repeats, ctx, with_cpu=True)
+    del primary
+    gc.collect()
+    torch.cuda.empty_cache()
 
-    def barrier():
-        if world > 1:
-            dist.barrier()
-        torch.cuda.synchronize()
-
-    for _ in range(args.warmup):
-        wl.step()
-    barrier()
-    sampler = ClockSampler(local_rank)
-    start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    sampler.start()
-    start.record(stream)
-    for _ in range(args.steps):
-        wl.step()
-    stop.record(stream)
-    barrier()
-    clocks = sampler.stop()
-    ms_total = start.elapsed_time(stop)
-
-    # end to end through the public operator with host buffers: pinned H2D of the step's inputs,
-    # the step, D2H of its result - all inside the timed region
-    e2e_steps = args.e2e_steps or min(args.steps, 5)
-    e2e_ms = None
-    wl.h2d = wl.d2h = 0
-    if not args.capture:
-        wl.e2e_setup(torch)
-        wl.e2e_step()
-        barrier()
-        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        e0.record(stream)
-        for _ in range(e2e_steps):
-            wl.e2e_step()
-        e1.record(stream)
-        barrier()
-        e2e_ms = e0.elapsed_time(e1) / e2e_steps
-
-    if world > 1:
-        t = torch.tensor([ms_total, e2e_ms or 0.0], device=device, dtype=torch.float64)
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-        ms_total, e2e_ms = float(t[0]), (float(t[1]) if e2e_ms is not None else None)
-    ms_step = ms_total / args.steps
-    work = wl.work_per_step()
-    scale = 1e9 if wl.unit == "GB/s" else 1e12
-    strong = getattr(wl, "scaling", "weak") == "strong"   # strong: `work` is already the whole job
-    value = work / (ms_step * 1e-3) / scale * (1 if strong else world)
-    per_gpu = value / world
-    e2e_value = (work / (e2e_ms * 1e-3) / scale * (1 if strong else world)) if e2e_ms else None
+    secondary = []
+    if not args.no_secondary and not args.capture:
+        cpu_done = set()
+        for make in secondary_factories:
+            wl = make()
+            # one CPU leg per workload family (the headline already carries the prefill one)
+            family = type(wl).__name__
+            with_cpu = family in ("DecodeWorkload", "PagedWorkload", "LongContextWorkload") and family not in cpu_done
+            cpu_done.add(family)
+            entry = measure(wl, args, wl.default_steps, repeats, ctx, with_cpu=with_cpu)
+            if entry is not None:
+                secondary.append(entry)
+            del wl
+            gc.collect()
+            torch.cuda.empty_cache()
 
     if rank == 0:
-        peaks = measured_peaks()
-        peak = peaks["hbm_gbs"] if wl.bound == "hbm" else peaks["tflops"]
-        nominal = NOMINAL_HBM_GBS if wl.bound == "hbm" else NOMINAL_TENSOR_TFLOPS
-        cpu = None
-        if not args.capture:
-            cw, cs, desc, kind = wl.cpu_sample(threads, "port")
-            cpu = {"value": cw / cs / scale, "unit": wl.unit, "cores": threads, "kind": kind,
-                   "sample": desc + f" ({cs:.1f} s of FP64 host work)"}
         line = {
-            "metric": wl.metric, "value": value, "unit": wl.unit, "n_gpus": world, "steps": args.steps,
-            "warmup": args.warmup, "ms_per_step": ms_step, "higher_is_better": True, "scaling": getattr(wl, "scaling", "weak"),
-            "vs_baseline": None, "dtype": getattr(wl, "dtype_name", "bf16"),
+            "metric": head["metric"], "value": head["value"], "unit": head["unit"], "n_gpus": world, "steps": args.steps,
+            "warmup": args.warmup, "ms_per_step": head["ms_per_step"], "higher_is_better": True, "scaling": head["scaling"],
+            "vs_baseline": None, "dtype": head["dtype"],
             "data": "synthetic (seeded iid N(0,1), random page tables)",
-            "config": wl.config(),
-            "roofline": {"bound": wl.bound, "achieved": per_gpu, "peak": peak, "unit": wl.unit,
-                         "frac": per_gpu / peak, "peak_source": peaks["source"],
-                         "frac_of_nominal": per_gpu / nominal, "traffic": wl.traffic(),
-                         "traffic_unit": "bytes per launch of the dominant kernel (ncu capture, scaled; see profiles/)"},
-            "cpu_baseline": cpu,
-            "e2e": {"value": e2e_value, "unit": wl.unit, "h2d_bytes_per_step": wl.h2d, "d2h_bytes_per_step": wl.d2h,
-                    "ms_per_step": e2e_ms, "steps": e2e_steps},
-            "gpu_launches": wl.launches_per_step * args.steps,
-            "clocks": clocks,
+            "config": head["config"], "repeats": head["repeats"], "roofline": head["roofline"],
+            "cpu_baseline": head["cpu_baseline"], "e2e": head["e2e"],
+            "gpu_launches": head["gpu_launches"], "clocks": head["clocks"],
+            "host": {"numa_node_of_gpu": node, "threads": threads},
+            "secondary": secondary,
         }
         print(json.dumps(line), flush=True)
     if world > 1:
@@ -608,24 +907,25 @@ def reference_arm(args, rank, world, threads):
     if rank != 0:
         return
     import numpy as np
-
-    class _HostTorchShim:
-        """The CPU arm needs the workload's tensors but no GPU: build them with torch on the host."""
-
     import torch
-    LongContextWorkload.exchange = args.exchange
-    FlashWorkload.dtype_name = args.dtype
-    wl = WORKLOADS[args.workload]()
+    name = "flash" if args.workload == "all" else args.workload
+    wl = {"flash": lambda: FlashWorkload(args.dtype), "decode": DecodeWorkload, "paged": PagedWorkload,
+          "longctx": lambda: LongContextWorkload(exchange=args.exchange), "kvfill": None}[name]
+    if wl is None:
+        print(json.dumps({"impl": "reference", "unavailable": "the reference has no CPU implementation of the KV kernels"}), flush=True)
+        return
+    wl = wl()
     # host tensors with the workload's shapes, reduced to the sample the CPU leg consumes
     g = torch.Generator().manual_seed(args.seed)
     if isinstance(wl, FlashWorkload):
-        wl.q = torch.randn((1, HQ, wl.S, D), generator=g).to(torch.bfloat16)
-        wl.k = torch.randn((1, HKV, wl.S, D), generator=g).to(torch.bfloat16)
-        wl.v = torch.randn((1, HKV, wl.S, D), generator=g).to(torch.bfloat16)
+        wl.q = torch.randn((1, HQ, wl.S, wl.d), generator=g).to(torch.bfloat16)
+        wl.k = torch.randn((1, HKV, wl.S, wl.d), generator=g).to(torch.bfloat16)
+        wl.v = torch.randn((1, HKV, wl.S, wl.d), generator=g).to(torch.bfloat16)
     elif isinstance(wl, LongContextWorkload):
-        wl.q = torch.randn((1, HQ, 1, D), generator=g).to(torch.bfloat16)
-        wl.k = torch.randn((1, HKV, 16384, D), generator=g).to(torch.bfloat16)
-        wl.v = torch.randn((1, HKV, 16384, D), generator=g).to(torch.bfloat16)
+        wl.q = torch.randn((1, HQ, 1, wl.d), generator=g).to(torch.bfloat16)
+        wl.k = torch.randn((1, HKV, 16384, wl.d), generator=g).to(torch.bfloat16)
+        wl.v = torch.randn((1, HKV, 16384, wl.d), generator=g).to(torch.bfloat16)
+        wl.px, wl.world = None, 1
     elif isinstance(wl, DecodeWorkload):
         nb = max(1, min(wl.B, 8 * threads))
         wl.q = torch.randn((nb, HQ, 1, D), generator=g).to(torch.bfloat16)
@@ -634,7 +934,7 @@ def reference_arm(args, rank, world, threads):
     else:
         rng = np.random.default_rng(args.seed)
         wl.np, wl.torch = np, torch
-        wl.lens = rng.integers(512, 8193, size=wl.NSEQ).astype(np.int64)
+        wl.lens = wl.all_lens = rng.integers(512, 8193, size=wl.NSEQ).astype(np.int64)
         ns = max(1, min(wl.NSEQ, 2 * threads))
         need = int(sum(-(-(int(n) + 1) // wl.BS) for n in wl.lens[:ns]))
         wl.k_pool = torch.randn((need, wl.BS, HKV, D), generator=g).to(torch.bfloat16)
@@ -646,6 +946,7 @@ def reference_arm(args, rank, world, threads):
             for j in range(-(-(int(wl.lens[s]) + 1) // wl.BS)):
                 table[s, j] = perm.pop()
         wl.table_host = table
+    wl.sets = [None]
     scale = 1e9 if wl.unit == "GB/s" else 1e12
     for _ in range(min(args.warmup, 1)):
         wl.cpu_sample(threads, "reference")

@@ -270,33 +270,32 @@ const DispatchThresholds kDispatch{
     /* revision             */ "b200-r1",
 };
 
-// The decode kernel runs one wave of resident CTAs (2 per SM) and hands each an equal, contiguous share of the
-// 64-token steps of all (sequence, kv head, head chunk) units; a unit cut by CTA boundaries yields one partial per
-// piece. The split count is therefore the number of partial SLOTS per row: the pieces the longest unit can be cut
-// into, plus one for a share that starts in its middle. Fewer slots than that only make the kernel use larger
-// shares (fewer busy CTAs), never a wrong result.
-int64_t SlotsForSchedule(int64_t total_steps, int64_t longest_steps, int64_t sm_count) {
-    if (total_steps <= 0 || longest_steps <= 1) return 1;
-    const int64_t ctas = 2 * (sm_count > 0 ? sm_count : 148);
-    const int64_t per_cta = detail::Max<int64_t>(1, detail::CeilDiv<int64_t>(total_steps, ctas));
+// The decode kernel runs one wave of resident CTAs (2 per SM). Every (kv head, head chunk) column gets the same
+// number of them, and they split the column's list of 64-token steps (sequence after sequence) into equal contiguous
+// shares; a sequence cut by share boundaries yields one partial per piece. The split count is therefore the number of
+// partial SLOTS per row: the pieces the longest sequence can be cut into, plus one for a share that starts in its
+// middle. Fewer slots than that only make the kernel use larger shares (fewer busy CTAs), never a wrong result.
+int64_t SlotsForSchedule(int64_t column_steps, int64_t longest_steps, int64_t columns, int64_t sm_count) {
+    if (column_steps <= 0 || longest_steps <= 1) return 1;
+    const int64_t resident = 2 * (sm_count > 0 ? sm_count : 148);
+    const int64_t sharers = detail::Max<int64_t>(1, resident / detail::Max<int64_t>(1, columns));
+    const int64_t per_cta = detail::Max<int64_t>(1, detail::CeilDiv<int64_t>(column_steps, sharers));
     const int64_t slots = detail::CeilDiv<int64_t>(longest_steps, per_cta) + 1;
     return detail::Max<int64_t>(2, detail::Min(slots, kDispatch.max_splits));
 }
 
 int64_t DecodeSplitsFor(int64_t seq_kv, int64_t batch, int64_t kv_heads, int64_t group, int64_t sm_count) {
     if (seq_kv <= 0) return 1;
-    const int64_t units = detail::Max<int64_t>(1, batch * kv_heads * ((group + 15) / 16));
     const int64_t steps = detail::CeilDiv<int64_t>(seq_kv, kDecodeStepTokens);
-    return SlotsForSchedule(units * steps, steps, sm_count);
+    return SlotsForSchedule(detail::Max<int64_t>(1, batch) * steps, steps, kv_heads * ((group + 15) / 16), sm_count);
 }
 
 // Ragged batches: `typical_len` is the mean length; the longest sequence is taken as twice that (exact callers use
 // SlotsForSchedule with the true lengths).
 int64_t PagedSplitsFor(int64_t typical_len, int64_t num_seqs, int64_t kv_heads, int64_t group, int64_t sm_count) {
     if (typical_len <= 0) return 1;
-    const int64_t units = detail::Max<int64_t>(1, num_seqs * kv_heads * ((group + 15) / 16));
     const int64_t steps = detail::CeilDiv<int64_t>(typical_len, kDecodeStepTokens);
-    return SlotsForSchedule(units * steps, 2 * steps, sm_count);
+    return SlotsForSchedule(detail::Max<int64_t>(1, num_seqs) * steps, 2 * steps, kv_heads * ((group + 15) / 16), sm_count);
 }
 
 }  // namespace tables

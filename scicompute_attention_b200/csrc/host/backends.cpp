@@ -634,7 +634,7 @@ sci::Result<AttentionResult> RunPaged(const sci::Tensor& q, const PagedKVCache& 
     if (cfg.num_splits > 0) {
         splits = detail::Min<int64_t>(cfg.num_splits, tables::kDispatch.max_splits);
     } else {
-        const int64_t units_per_seq = kcfg.num_kv_heads * ((heads / kcfg.num_kv_heads + 15) / 16);
+        const int64_t columns = kcfg.num_kv_heads * ((heads / kcfg.num_kv_heads + 15) / 16);
         const int64_t row_tokens = detail::Min<int64_t>(upper, max_blocks * block_size);
         int64_t total_steps = 0, longest_steps = 0;
         for (int64_t s = 0; s < num_seqs; ++s) {
@@ -643,7 +643,7 @@ sci::Result<AttentionResult> RunPaged(const sci::Tensor& q, const PagedKVCache& 
             total_steps += steps;
             longest_steps = detail::Max(longest_steps, steps);
         }
-        splits = tables::SlotsForSchedule(total_steps * units_per_seq, longest_steps, DeviceCapability::ForDevice(0).sm_count);
+        splits = tables::SlotsForSchedule(total_steps, longest_steps, columns, DeviceCapability::ForDevice(0).sm_count);
     }
     const int64_t elements = tables::PartialElements(num_seqs, heads, splits, d);
     const sci::Result<float*> scratch =

@@ -55,7 +55,7 @@ extern const DispatchThresholds kDispatch;
 
 // Split-K policy (B200): number of partial slots per row for the decode kernel's equal-share schedule.
 constexpr int64_t kDecodeStepTokens = 64;  // tokens one CTA consumes per step (4 warps x 16)
-int64_t SlotsForSchedule(int64_t total_steps, int64_t longest_steps, int64_t sm_count);
+int64_t SlotsForSchedule(int64_t column_steps, int64_t longest_steps, int64_t columns, int64_t sm_count);
 int64_t DecodeSplitsFor(int64_t seq_kv, int64_t batch, int64_t kv_heads, int64_t group, int64_t sm_count);
 int64_t PagedSplitsFor(int64_t typical_len, int64_t num_seqs, int64_t kv_heads, int64_t group, int64_t sm_count);
 inline int64_t PartialElements(int64_t batch, int64_t heads, int64_t splits, int64_t head_dim) {

@@ -365,14 +365,16 @@ __device__ __forceinline__ void MarkUnusedSlots(const ScaDecodeFwdParams& p, int
 
 // The split-K partial kernel, scheduled for an equal share of the K/V stream per CTA.
 //
-// The work is the list of kSpan-token steps of every (sequence, kv head, head chunk), sequence-major. The grid is one
-// wave of resident CTAs and CTA c takes steps [c * per_cta, (c + 1) * per_cta) of that list - a contiguous stretch that
-// may start and end in the middle of a sequence and may cover several short ones. Every piece of a sequence a CTA
-// holds is one "segment" and yields one partial; the pieces of one sequence sit in consecutive CTAs, so the segment's
-// slot in the [rows, num_splits] partial arrays is the distance to the first CTA that touches the sequence.
-// per_cta is never smaller than longest_sequence / (num_splits - 1) steps, which bounds the pieces of any sequence by
-// num_splits; slots that stay unused are marked empty by the CTA that holds the sequence's first step.
-// With num_splits == 1 a CTA takes whole (sequence, kv head, head chunk) units instead.
+// The grid is one wave of resident CTAs, a multiple of the number of (kv head, head chunk) columns. CTA c works on
+// column c % columns for its whole life; the CTAs of one column split that column's list of kSpan-token steps
+// (sequence after sequence) into equal contiguous shares. Neighbouring CTAs therefore read the same tokens of
+// neighbouring kv heads at about the same time - in a paged pool those are adjacent 2*D-byte pieces of one token row.
+// A share may start and end in the middle of a sequence and may cover several short ones; every piece of a sequence
+// a CTA holds is one "segment" and yields one partial. The pieces of one sequence sit in consecutive CTAs of the
+// column, so a segment's slot in the [rows, num_splits] partial arrays is the distance to the first CTA that touches
+// the sequence. A share is never smaller than longest_sequence / (num_splits - 1) steps, which bounds the pieces of
+// any sequence by num_splits (with num_splits == 1 shares are made of whole sequences); slots that stay unused are
+// marked empty by the CTA that holds the sequence's first step.
 // Sequence lengths are read on the device (seq_lens), so the schedule needs no host knowledge of a ragged batch.
 template <typename T, int D, bool kPaged, bool kHi>
 __global__ void __launch_bounds__(kThreads)
@@ -382,36 +384,33 @@ decode_partial_kernel(const ScaDecodeFwdParams p, const int head_chunks) {
     __shared__ int64_t s_found[2];
     const int lane = threadIdx.x & 31;
     const int warp = threadIdx.x >> 5;
-    const int64_t units_per_seq = p.num_kv_heads * head_chunks;  // (kv head, head chunk) pairs
+    const int columns = static_cast<int>(p.num_kv_heads) * head_chunks;
+    // grids smaller than the number of columns let every CTA walk several columns, each as its only CTA
+    const int sharers = gridDim.x >= static_cast<unsigned>(columns) ? static_cast<int>(gridDim.x) / columns : 1;
+    const int share = gridDim.x >= static_cast<unsigned>(columns) ? static_cast<int>(blockIdx.x) / columns : 0;
+    const int first_column = gridDim.x >= static_cast<unsigned>(columns) ? static_cast<int>(blockIdx.x) % columns
+                                                                         : static_cast<int>(blockIdx.x);
+    const int column_stride = gridDim.x >= static_cast<unsigned>(columns) ? columns : static_cast<int>(gridDim.x);
+    if (share >= sharers) return;  // a grid that is no multiple of the column count
 
-    if (p.num_splits == 1) {
-        asm volatile("griddepcontrol.launch_dependents;\n" ::: "memory");
-        const int64_t units = p.batch * units_per_seq;
-        const int64_t u0 = units * blockIdx.x / gridDim.x, u1 = units * (blockIdx.x + 1) / gridDim.x;
-        for (int64_t u = u0; u < u1; ++u) {
-            const int64_t b = u / units_per_seq;
-            const int gi = static_cast<int>(u % units_per_seq);
-            DecodeSegment<T, D, kPaged, kHi>(p, smem, b, gi / head_chunks, gi % head_chunks, 0, SeqLen<kPaged>(p, b), 0);
-        }
-        return;
-    }
-
+    // ---- this CTA's share [begin, end) of a column's step list, and the sequence that holds `begin` ----------
     int64_t b, before, len, steps, per_cta, begin, end;
     if (p.seq_lens == nullptr) {
         // every sequence has the same length: the list is regular and needs no look at device memory
         len = SeqLen<kPaged>(p, 0);
         steps = StepsFor(len);
-        const int64_t total = p.batch * steps * units_per_seq;
-        per_cta = (total + gridDim.x - 1) / gridDim.x;
-        const int64_t by_slots = (steps + p.num_splits - 2) / (p.num_splits - 1);
-        if (per_cta < by_slots) per_cta = by_slots;
-        begin = static_cast<int64_t>(blockIdx.x) * per_cta;
+        const int64_t total = p.batch * steps;
+        per_cta = (total + sharers - 1) / sharers;
+        const int64_t floor_steps = p.num_splits > 1 ? (steps + p.num_splits - 2) / (p.num_splits - 1) : total;
+        if (per_cta < floor_steps) per_cta = floor_steps;
+        if (p.num_splits == 1) per_cta = ((per_cta + steps - 1) / steps) * steps;  // whole sequences only
+        begin = share * per_cta;
         if (begin >= total) return;
         end = begin + per_cta < total ? begin + per_cta : total;
-        b = begin / (steps * units_per_seq);
+        b = begin / steps;
         before = b * steps;
     } else {
-        // ---- pass 1: total steps and the longest sequence ------------------------------------------
+        // pass 1: total steps and the longest sequence
         int64_t sum = 0, longest = 0;
         for (int64_t i = threadIdx.x; i < p.batch; i += kThreads) {
             const int64_t t = StepsFor(SeqLen<kPaged>(p, i));
@@ -436,20 +435,19 @@ decode_partial_kernel(const ScaDecodeFwdParams p, const int head_chunks) {
             sum += s_part[w][0];
             longest = s_part[w][1] > longest ? s_part[w][1] : longest;
         }
-        const int64_t total = sum * units_per_seq;
-        per_cta = (total + gridDim.x - 1) / gridDim.x;
-        const int64_t by_slots = (longest + p.num_splits - 2) / (p.num_splits - 1);
-        if (per_cta < by_slots) per_cta = by_slots;
-        begin = static_cast<int64_t>(blockIdx.x) * per_cta;
+        const int64_t total = sum;
+        per_cta = (total + sharers - 1) / sharers;
+        // with one slot a share must end where a sequence ends: the whole column then goes to its first CTA
+        const int64_t floor_steps = p.num_splits > 1 ? (longest + p.num_splits - 2) / (p.num_splits - 1) : total;
+        if (per_cta < floor_steps) per_cta = floor_steps;
+        begin = share * per_cta;
         if (begin >= total) return;
         end = begin + per_cta < total ? begin + per_cta : total;
 
-        // ---- pass 2: the sequence that holds step `begin` ------------------------------------------
-        // steps before sequence i: units_per_seq * before[i]; find i with before[i] <= begin / units_per_seq < before[i + 1]
-        const int64_t want = begin / units_per_seq;
+        // pass 2: find i with before[i] <= begin < before[i] + steps[i]
         int64_t running = 0;
         __syncthreads();
-        for (int64_t base = 0; base < p.batch && running <= want; base += kThreads) {
+        for (int64_t base = 0; base < p.batch && running <= begin; base += kThreads) {
             const int64_t i = base + threadIdx.x;
             const int64_t t = i < p.batch ? StepsFor(SeqLen<kPaged>(p, i)) : 0;
             int64_t incl = t;
@@ -467,7 +465,7 @@ decode_partial_kernel(const ScaDecodeFwdParams p, const int head_chunks) {
                 if (w < warp) mine += s_part[w][0];
                 chunk_total += s_part[w][0];
             }
-            if (t > 0 && mine <= want && want < mine + t) {
+            if (t > 0 && mine <= begin && begin < mine + t) {
                 s_found[0] = i;
                 s_found[1] = mine;
             }
@@ -475,36 +473,40 @@ decode_partial_kernel(const ScaDecodeFwdParams p, const int head_chunks) {
             __syncthreads();
         }
         b = s_found[0];
-        before = s_found[1];  // steps of one unit column before sequence b
+        before = s_found[1];  // steps of this column before sequence b
         len = SeqLen<kPaged>(p, b);
         steps = StepsFor(len);
     }
     // the merge kernel that follows on the stream may be set up while this grid streams K/V
     asm volatile("griddepcontrol.launch_dependents;\n" ::: "memory");
 
-    // ---- walk the stretch segment by segment --------------------------------------------------------
-    int64_t pos = begin;
-    while (pos < end) {
-        const int64_t in_seq = pos - units_per_seq * before;  // offset inside sequence b's steps
-        const int gi = static_cast<int>(in_seq / steps);
-        const int64_t t0 = in_seq % steps;
-        const int64_t unit_start = units_per_seq * before + gi * steps;
-        int64_t t1 = t0 + (end - pos);
-        if (t1 > steps) t1 = steps;
-        const int hk = gi / head_chunks, hc = gi % head_chunks;
-        const int slot = static_cast<int>(blockIdx.x - unit_start / per_cta);
-        if (t0 == 0) {
-            const int used = static_cast<int>((unit_start + steps - 1) / per_cta - unit_start / per_cta) + 1;
-            MarkUnusedSlots(p, b, hk, hc, used);
-        }
-        const int64_t j_end = t1 * kSpan < len ? t1 * kSpan : len;
-        DecodeSegment<T, D, kPaged, kHi>(p, smem, b, hk, hc, t0 * kSpan, j_end, slot);
-        pos += t1 - t0;
-        if (t1 == steps && gi == units_per_seq - 1 && pos < end) {
-            before += steps;
-            ++b;
-            len = SeqLen<kPaged>(p, b);
-            steps = StepsFor(len);
+    // ---- walk the share segment by segment, in every column this CTA serves -----------------------------
+    const int64_t b_first = b, before_first = before, len_first = len, steps_first = steps;
+    for (int column = first_column; column < columns; column += column_stride) {
+        const int hk = column / head_chunks, hc = column % head_chunks;
+        b = b_first;
+        before = before_first;
+        len = len_first;
+        steps = steps_first;
+        int64_t pos = begin;
+        while (pos < end) {
+            const int64_t t0 = pos - before;
+            int64_t t1 = t0 + (end - pos);
+            if (t1 > steps) t1 = steps;
+            const int slot = static_cast<int>(share - before / per_cta);
+            if (t0 == 0) {
+                const int used = static_cast<int>((before + steps - 1) / per_cta - before / per_cta) + 1;
+                MarkUnusedSlots(p, b, hk, hc, used);
+            }
+            const int64_t j_end = t1 * kSpan < len ? t1 * kSpan : len;
+            DecodeSegment<T, D, kPaged, kHi>(p, smem, b, hk, hc, t0 * kSpan, j_end, slot);
+            pos += t1 - t0;
+            if (t1 == steps && pos < end) {
+                before += steps;
+                ++b;
+                len = SeqLen<kPaged>(p, b);
+                steps = StepsFor(len);
+            }
         }
     }
 }
@@ -598,11 +600,18 @@ int LaunchPartial(const ScaDecodeFwdParams& p, int head_chunks, cudaStream_t str
         }
         resident_per_sm = n;
     }
-    const int64_t units = p.batch * p.num_kv_heads * head_chunks;
+    const int64_t columns = p.num_kv_heads * head_chunks;
+    const int64_t resident = static_cast<int64_t>(SmCount()) * resident_per_sm;
     const int64_t upper = kPaged ? p.max_blocks_per_seq * p.block_size : p.seq_kv;
     const int64_t steps = std::max<int64_t>(1, (std::min(p.seq_kv, upper) + kSpan - 1) / kSpan);
-    const int64_t work = p.num_splits == 1 ? units : units * steps;  // upper bound on the steps of the list
-    const int64_t blocks = std::max<int64_t>(1, std::min<int64_t>(static_cast<int64_t>(SmCount()) * resident_per_sm, work));
+    // CTAs per column: as many as stay resident, never more than the column has steps (or sequences, with one slot)
+    const int64_t useful = p.num_splits == 1 ? p.batch : p.batch * steps;
+    int64_t blocks;
+    if (resident >= columns) {
+        blocks = columns * std::max<int64_t>(1, std::min(resident / columns, useful));
+    } else {
+        blocks = resident;  // more columns than resident CTAs: every CTA walks several columns
+    }
     decode_partial_kernel<T, D, kPaged, kHi>
         <<<static_cast<unsigned>(blocks), kThreads, G::kSmemBytes, stream>>>(p, head_chunks);
     return CheckLaunch("decode_partial_kernel", stream);

@@ -67,16 +67,17 @@ def acquire_scratch_fp32(elements: int, device: torch.device, kind: int = 1) -> 
 DECODE_STEP_TOKENS = 64  # tokens one CTA of the decode kernel consumes per step (4 warps x 16)
 
 
-def slots_for_schedule(total_steps: int, longest_steps: int, sms: int) -> int:
-    """Partial slots per row for the decode kernel's schedule: one wave of resident CTAs (2 per SM), each with an
-    equal, contiguous share of the 64-token steps of all (sequence, kv head, head chunk) units; a unit cut by CTA
-    boundaries yields one partial per piece. Needed: the pieces of the longest unit, plus one for a share that starts
-    in its middle. (The reference's rule, one CTA per fixed split, is ceil(seq_kv / 512) capped at 16:
-    src/backends/decode/decode_config.hpp:24-31.)"""
-    if total_steps <= 0 or longest_steps <= 1:
+def slots_for_schedule(column_steps: int, longest_steps: int, columns: int, sms: int) -> int:
+    """Partial slots per row for the decode kernel's schedule: one wave of resident CTAs (2 per SM), the same number
+    for every (kv head, head chunk) column; the CTAs of a column split its list of 64-token steps (sequence after
+    sequence) into equal contiguous shares, and a sequence cut by share boundaries yields one partial per piece.
+    Needed: the pieces of the longest sequence, plus one for a share that starts in its middle. (The reference's rule,
+    one CTA per fixed split, is ceil(seq_kv / 512) capped at 16: src/backends/decode/decode_config.hpp:24-31.)"""
+    if column_steps <= 0 or longest_steps <= 1:
         return 1
-    ctas = 2 * (sms if sms > 0 else 148)
-    per_cta = max(1, -(-total_steps // ctas))
+    resident = 2 * (sms if sms > 0 else 148)
+    sharers = max(1, resident // max(1, columns))
+    per_cta = max(1, -(-column_steps // sharers))
     return max(2, min(-(-longest_steps // per_cta) + 1, MAX_SPLITS))
 
 
@@ -84,9 +85,8 @@ def splits_for(seq_kv: int, batch: int, num_kv_heads: int, group: int, sms: int)
     """Automatic slot count for equally long sequences."""
     if seq_kv <= 0:
         return 1
-    units = max(1, batch * num_kv_heads * ((group + 15) // 16))
     steps = -(-seq_kv // DECODE_STEP_TOKENS)
-    return slots_for_schedule(units * steps, steps, sms)
+    return slots_for_schedule(max(1, batch) * steps, steps, num_kv_heads * ((group + 15) // 16), sms)
 
 
 def paged_splits_for(typical_len: int, num_seqs: int, num_kv_heads: int, group: int, sms: int, longest_len: int = 0) -> int:
@@ -94,10 +94,9 @@ def paged_splits_for(typical_len: int, num_seqs: int, num_kv_heads: int, group: 
     unless `longest_len` says otherwise."""
     if typical_len <= 0:
         return 1
-    units = max(1, num_seqs * num_kv_heads * ((group + 15) // 16))
     steps = -(-typical_len // DECODE_STEP_TOKENS)
     longest = -(-longest_len // DECODE_STEP_TOKENS) if longest_len > 0 else 2 * steps
-    return slots_for_schedule(units * steps, longest, sms)
+    return slots_for_schedule(max(1, num_seqs) * steps, longest, num_kv_heads * ((group + 15) // 16), sms)
 
 
 def _strides(layout: str, seq: int, heads: int, d: int) -> tuple[int, int, int]:
@@ -169,17 +168,16 @@ def decode_attention(q, k, v, *, scale=None, num_splits: int = 0, layout: str = 
 
 
 def paged_attention(q, k_pool, v_pool, page_table, seq_lens, *, block_size: int, scale=None,
-                    num_splits: int = 0, typical_len: int = 0, stream=None, return_stats: bool = False,
-                    seq_order=None):
-    """Decode over page-table-indirected K/V (sca::paged_attention). seq_order (device int32 [num_seqs], a
-    permutation) is an optional scheduling hint: thread blocks are handed out in that order, longest first
-    shortens the tail of a ragged batch.
+                    num_splits: int = 0, typical_len: int = 0, longest_len: int = 0, stream=None,
+                    return_stats: bool = False, seq_order=None):
+    """Decode over page-table-indirected K/V (sca::paged_attention).
 
     q [num_seqs, H_q, 1, D]; pools [num_blocks, block_size, H_kv, D]; page_table int32
     [num_seqs, max_blocks_per_seq] on the device (-1 = unmapped); seq_lens int32 [num_seqs] on the
     device or None (every sequence then scans max_blocks_per_seq * block_size positions).
-    `typical_len` is an optional host-side hint (e.g. the mean sequence length the cache object
-    already tracks) used only to choose the split count."""
+    `typical_len` / `longest_len` are optional host-side hints (the mean and the maximum sequence length, which a
+    cache object tracks anyway) used only to size the partial scratch: enough slots for an even schedule. seq_order
+    is accepted for compatibility and ignored: the kernel balances the work itself."""
     _require_cuda(q, k_pool, v_pool, page_table, seq_lens)
     if q.dim() != 4:
         raise _lib.ScaError(4, f"paged_attention expects q=[num_seqs, H_q, seq_q, D]; got ndims={q.dim()}")
@@ -197,7 +195,7 @@ def paged_attention(q, k_pool, v_pool, page_table, seq_lens, *, block_size: int,
         splits = min(num_splits, MAX_SPLITS)
     else:
         splits = paged_splits_for(typical_len if typical_len > 0 else min(upper, max_blocks * bs), s, hkv,
-                                  hq // hkv, sm_count(q.device))
+                                  hq // hkv, sm_count(q.device), longest_len)
     base = s * hq * splits
     ws = acquire_scratch_fp32(base * (2 + d), q.device)
     out = torch.empty((s, hq, 1, d), dtype=q.dtype, device=q.device)
