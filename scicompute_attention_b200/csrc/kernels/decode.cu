@@ -22,6 +22,7 @@
 // Algorithmic HBM traffic per token and kv head: 2 * D * sizeof(T) bytes (K row + V row), read once.
 #include <algorithm>
 #include <mutex>
+#include <type_traits>
 
 #include "common.cuh"
 
@@ -47,6 +48,10 @@ struct DecodeGeom {
     static_assert(D % 32 == 0, "head_dim must be a multiple of 32");
     static_assert(kWarpBytes >= (32 + 16 * D) * 4, "merge staging must fit in the warp's ring");
 };
+
+__device__ __forceinline__ float2 Unpack2Bf16(uint32_t v) {
+    return make_float2(__uint_as_float(v << 16), __uint_as_float(v & 0xffff0000u));
+}
 
 // K fragments: a phase of 8 lanes reads rows {r, r+1} x 4 adjacent chunks -> flip bit 2 on odd rows.
 template <bool kSwizzle>
@@ -84,6 +89,9 @@ __device__ __forceinline__ void DecodeSegment(const ScaDecodeFwdParams& p, unsig
                                               const int slot) {
     using G = DecodeGeom<D>;
     constexpr int CPR = G::kChunksPerRow;
+    // bf16 keeps 8 bits of a probability: rounding P alone would cost about 1e-3 of relative L2 error in the output.
+    // The kernel is bound by HBM, not by the tensor pipe, so P goes into the P V product as two bf16 terms.
+    constexpr bool kSplitP = std::is_same<T, __nv_bfloat16>::value;
     const int lane = threadIdx.x & 31;
     const int warp = threadIdx.x >> 5;
     const int g = lane >> 2;  // fragment row / token slot
@@ -225,7 +233,7 @@ __device__ __forceinline__ void DecodeSegment(const ScaDecodeFwdParams& p, unsig
                         s[t][e] = ok ? s[t][e] * scale_log2 : -CUDART_INF_F;
                     }
                 }
-                uint32_t pa[4];
+                uint32_t pa[4], pb[4];
                 float alpha[2];
 #pragma unroll
                 for (int h = 0; h < 2; ++h) {
@@ -233,6 +241,8 @@ __device__ __forceinline__ void DecodeSegment(const ScaDecodeFwdParams& p, unsig
                         alpha[1] = 1.0f;
                         pa[1] = 0u;
                         pa[3] = 0u;
+                        pb[1] = 0u;
+                        pb[3] = 0u;
                         continue;
                     }
                     float mx = fmaxf(fmaxf(s[0][2 * h], s[0][2 * h + 1]), fmaxf(s[1][2 * h], s[1][2 * h + 1]));
@@ -249,6 +259,12 @@ __device__ __forceinline__ void DecodeSegment(const ScaDecodeFwdParams& p, unsig
                     m_run[h] = m_new;
                     pa[h] = Pack2<T>(p00, p01);      // rows g / g+8, tokens 2c, 2c+1
                     pa[2 + h] = Pack2<T>(p10, p11);  // tokens 8+2c, 8+2c+1
+                    if (kSplitP) {
+                        // what the 8-bit mantissa dropped, as a second bf16 operand: P = P_hi + P_lo to 2^-16
+                        const float2 h0 = Unpack2Bf16(pa[h]), h1 = Unpack2Bf16(pa[2 + h]);
+                        pb[h] = Pack2<T>(p00 - h0.x, p01 - h0.y);
+                        pb[2 + h] = Pack2<T>(p10 - h1.x, p11 - h1.y);
+                    }
                 }
                 // O = alpha * O + P V
 #pragma unroll
@@ -278,6 +294,7 @@ __device__ __forceinline__ void DecodeSegment(const ScaDecodeFwdParams& p, unsig
                             o[r][j][3] *= alpha[1];
                         }
                         MmaM16N8K16<T>(o[r][j], pa[0], pa[1], pa[2], pa[3], b0, b1);
+                        if (kSplitP) MmaM16N8K16<T>(o[r][j], pb[0], pb[1], pb[2], pb[3], b0, b1);
                     }
                 }
             }

@@ -82,6 +82,18 @@ template <>
 __device__ __forceinline__ float2 Unpack2<__half>(uint32_t v) {
     return __half22float2(*reinterpret_cast<const __half2*>(&v));
 }
+// bf16 inputs: the probabilities are handed to the P V product as fp16, not bf16. They lie in [0, 2^8], where fp16
+// resolves 2^-11 relative against 2^-8 - with bf16 the rounding of P alone costs about 1e-3 of relative L2 error in
+// the output. The tensor core wants both operands of one product in the same 16-bit format (a descriptor that mixes
+// them raises "illegal instruction" on sm_100a), so for bf16 inputs a small kernel first rewrites V as fp16 into a
+// stream-ordered temporary (values beyond the fp16 range saturate) and the prefill kernel reads V from there.
+// (Rewriting the V tiles in shared memory by the two idle warps was measured too: 7 % slower than this, because
+// the extra instructions land on two of the four schedulers the softmax warps run on.)
+template <typename T>
+struct PvFormat {
+    using type = __half;
+    static constexpr bool kConvertV = std::is_same<T, __nv_bfloat16>::value;
+};
 constexpr int kFlashThreads = 384;   // warp 0 TMA, 1 MMA, 2 TMEM owner, 3 idle, 4-7 / 8-11 softmax
 constexpr int kTmemColumns = 512;
 constexpr float kRescaleThreshold = 8.0f;  // log2 domain: P stays <= 2^8
@@ -158,6 +170,8 @@ flash_fwd_sm100_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
     constexpr int kQEmpty = kODone + 2;             // [2]
     constexpr int kOFree = kQEmpty + 2;             // [2]
     constexpr int kNumBars = kOFree + 2;
+    using PT = typename PvFormat<T>::type;
+    constexpr bool kCvtV = PvFormat<T>::kConvertV;
     static_assert(kNumBars * 8 + 16 <= G::kBarrierBytes, "barrier area too small");
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(smem + (bar_base - smem_base) + kNumBars * 8);
     volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
@@ -313,8 +327,11 @@ flash_fwd_sm100_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
         // ================================ MMA issuer ================================================
         if (lane == 0) {
             constexpr uint32_t fmt = std::is_same<T, __half>::value ? kFmtF16 : kFmtBf16;
-            constexpr uint32_t idesc_s = MakeInstrDesc(fmt, 0, 0, kBlockM, BN);  // Q K^T: both K-major
-            constexpr uint32_t idesc_o = MakeInstrDesc(fmt, 0, 1, kBlockM, DP);  // P V: V is MN-major
+            constexpr uint32_t idesc_s = MakeInstrDesc(fmt, fmt, 0, 0, kBlockM, BN);  // Q K^T: both K-major
+            // P V: V is MN-major; both operands in the P V format (fp16 also for bf16 inputs, see PvFormat: V then
+            // comes from the fp16 copy map_v points at)
+            constexpr uint32_t fmt_pv = kCvtV ? kFmtF16 : fmt;
+            constexpr uint32_t idesc_o = MakeInstrDesc(fmt_pv, fmt_pv, 0, 1, kBlockM, DP);
             // Descriptors are built once and advanced by compile-time constants, so that issuing one
             // tcgen05.mma costs a handful of instructions (this thread alone has to keep the tensor pipe fed).
             const uint64_t kmajor_hi = MakeSmemDesc(0, 16, 1024);                 // K-major operands (Q and K)
@@ -556,8 +573,8 @@ flash_fwd_sm100_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
                             TmemWaitLd();
     #pragma unroll
                             for (int i = 0; i < 32; ++i) {
-                                const float2 f = Unpack2<T>(q[i]);
-                                q[i] = Pack2<T>(f.x * alpha, f.y * alpha);
+                                const float2 f = Unpack2<PT>(q[i]);
+                                q[i] = Pack2<PT>(f.x * alpha, f.y * alpha);
                             }
                             TmemSt32(s_addr, q);
                         }
@@ -576,8 +593,8 @@ flash_fwd_sm100_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
                         const float2 eb = make_float2(Exp2(xb.x), Exp2(xb.y));
                         sum_a = Add2(sum_a, ea);
                         sum_b = Add2(sum_b, eb);
-                        pk[i / 2] = Pack2<T>(ea.x, ea.y);
-                        pk[16 + i / 2] = Pack2<T>(eb.x, eb.y);
+                        pk[i / 2] = Pack2<PT>(ea.x, ea.y);
+                        pk[16 + i / 2] = Pack2<PT>(eb.x, eb.y);
                     }
                     part4[0] = sum_a.x;
                     part4[1] = sum_a.y;
@@ -647,7 +664,66 @@ flash_fwd_sm100_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
     }
 }
 
+// V [batch, heads, seq, D] (any strides, bf16) -> compact fp16 [batch, heads, seq, D]; 8 elements per thread.
+__global__ void __launch_bounds__(256) flash_v_to_f16_kernel(const __nv_bfloat16* __restrict__ v, __half* __restrict__ out,
+                                                              int64_t batch, int64_t heads, int64_t seq, int64_t head_dim,
+                                                              int64_t sb, int64_t sh, int64_t ss) {
+    const int64_t chunks_per_row = head_dim / 8;
+    const int64_t total = batch * heads * seq * chunks_per_row;
+    for (int64_t i = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x; i < total;
+         i += static_cast<int64_t>(gridDim.x) * blockDim.x) {
+        int64_t rest = i;
+        const int64_t c = rest % chunks_per_row;
+        rest /= chunks_per_row;
+        const int64_t s = rest % seq;
+        rest /= seq;
+        const int64_t h = rest % heads;
+        const int64_t b = rest / heads;
+        uint4 x = *reinterpret_cast<const uint4*>(v + b * sb + h * sh + s * ss + c * 8);
+        uint32_t* word = reinterpret_cast<uint32_t*>(&x);
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+            const float2 f = Unpack2<__nv_bfloat16>(word[e]);
+            // one instruction for both lanes; values beyond the fp16 range saturate instead of becoming inf
+            asm("cvt.rn.satfinite.f16x2.f32 %0, %1, %2;" : "=r"(word[e]) : "f"(f.y), "f"(f.x));
+        }
+        reinterpret_cast<uint4*>(out)[i] = x;
+    }
+}
+
 // ---- host side -----------------------------------------------------------------------------------------
+constexpr int kMaxStatusDevices = 64;
+
+// Stream-ordered temporaries come from a pool of this library's own (one per device, created on first use) that keeps
+// what is freed: the default pool hands its memory back to the driver at every synchronisation, after which the next
+// allocation costs a trip to the driver again.
+cudaMemPool_t TemporaryPool() {
+    static std::mutex mu;
+    static cudaMemPool_t pools[kMaxStatusDevices] = {};
+    int device = 0;
+    if (cudaGetDevice(&device) != cudaSuccess || device < 0 || device >= kMaxStatusDevices) {
+        cudaGetLastError();
+        return nullptr;
+    }
+    std::lock_guard<std::mutex> lock(mu);
+    if (pools[device] == nullptr) {
+        cudaMemPoolProps props{};
+        props.allocType = cudaMemAllocationTypePinned;
+        props.handleTypes = cudaMemHandleTypeNone;
+        props.location.type = cudaMemLocationTypeDevice;
+        props.location.id = device;
+        cudaMemPool_t pool = nullptr;
+        if (cudaMemPoolCreate(&pool, &props) != cudaSuccess) {
+            cudaGetLastError();
+            return nullptr;
+        }
+        unsigned long long keep = ~0ull;
+        if (cudaMemPoolSetAttribute(pool, cudaMemPoolAttrReleaseThreshold, &keep) != cudaSuccess) cudaGetLastError();
+        pools[device] = pool;
+    }
+    return pools[device];
+}
+
 using EncodeTiledFn = CUresult (*)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
                                    const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
                                    CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
@@ -693,7 +769,6 @@ int MakeMap(CUtensorMap* map, const void* base, int dtype_id, int64_t d, int64_t
 
 // One host-visible word per device that a kernel sets when one of its bounded waits expires (1 + the warp that
 // gave up). The words live in one pinned, mapped, portable allocation; sca_flash_status reads and clears them.
-constexpr int kMaxStatusDevices = 64;
 
 int* ErrorWords(int** host_view) {
     static int* host = nullptr;
@@ -793,7 +868,38 @@ int LaunchFlash(const ScaFlashFwdParams& f, cudaStream_t stream, const VarlenWor
     CUtensorMap map_q, map_k, map_v;
     if (int rc = MakeMap(&map_q, f.q, f.dtype_id, f.head_dim, f.seq_q, f.num_heads, f.batch, f.q_ss, f.q_sh, f.q_sb, kBlockM, "q")) return rc;
     if (int rc = MakeMap(&map_k, f.k, f.dtype_id, f.head_dim, f.seq_kv, f.num_kv_heads, f.batch, f.k_ss, f.k_sh, f.k_sb, BN, "k")) return rc;
-    if (int rc = MakeMap(&map_v, f.v, f.dtype_id, f.head_dim, f.seq_kv, f.num_kv_heads, f.batch, f.v_ss, f.v_sh, f.v_sb, BN, "v")) return rc;
+    // bf16: V goes through an fp16 copy (PvFormat). The copy is a stream-ordered temporary, released behind the launch.
+    struct Temporary {
+        void* ptr = nullptr;
+        cudaStream_t stream = nullptr;
+        ~Temporary() {
+            if (ptr != nullptr && cudaFreeAsync(ptr, stream) != cudaSuccess) cudaGetLastError();
+        }
+    } v16;
+    if (PvFormat<T>::kConvertV) {
+        if (!Aligned16(f.v) || f.v_sb % 8 != 0 || f.v_sh % 8 != 0 || f.v_ss % 8 != 0 || f.head_dim % 8 != 0) {
+            return Fail(SCA_INVALID_ARGUMENT, "flash attention: v must be 16-byte aligned with strides that are multiples of 8 elements");
+        }
+        const int64_t elements = f.batch * f.num_kv_heads * f.seq_kv * f.head_dim;
+        v16.stream = stream;
+        cudaMemPool_t pool = TemporaryPool();
+        const cudaError_t e = pool != nullptr ? cudaMallocFromPoolAsync(&v16.ptr, static_cast<size_t>(elements) * 2, pool, stream)
+                                              : cudaMallocAsync(&v16.ptr, static_cast<size_t>(elements) * 2, stream);
+        if (e != cudaSuccess) {
+            v16.ptr = nullptr;
+            cudaGetLastError();
+            return FailCuda(e, "flash attention: cudaMallocAsync(fp16 copy of V)");
+        }
+        const int64_t threads_needed = elements / 8;
+        const unsigned blocks = static_cast<unsigned>(std::max<int64_t>(1, std::min<int64_t>((threads_needed + 255) / 256, static_cast<int64_t>(SmCount()) * 16)));
+        flash_v_to_f16_kernel<<<blocks, 256, 0, stream>>>(static_cast<const __nv_bfloat16*>(f.v), static_cast<__half*>(v16.ptr),
+                                                          f.batch, f.num_kv_heads, f.seq_kv, f.head_dim, f.v_sb, f.v_sh, f.v_ss);
+        if (int rc = CheckLaunch("flash_v_to_f16_kernel", stream)) return rc;
+        if (int rc = MakeMap(&map_v, v16.ptr, SCA_DTYPE_F16, f.head_dim, f.seq_kv, f.num_kv_heads, f.batch, f.head_dim,
+                             f.seq_kv * f.head_dim, f.num_kv_heads * f.seq_kv * f.head_dim, BN, "v (fp16 copy)")) return rc;
+    } else {
+        if (int rc = MakeMap(&map_v, f.v, f.dtype_id, f.head_dim, f.seq_kv, f.num_kv_heads, f.batch, f.v_ss, f.v_sh, f.v_sb, BN, "v")) return rc;
+    }
 
     FlashKernelParams p{};
     p.out = f.out;

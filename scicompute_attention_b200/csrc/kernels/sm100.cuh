@@ -127,10 +127,11 @@ __device__ __forceinline__ void TmemSt32(uint32_t taddr, const uint32_t (&r)[32]
 // ---- tcgen05.mma (dense f16/bf16 inputs, f32 accumulate, one CTA) -----------------------------------
 enum : uint32_t { kFmtF16 = 0, kFmtBf16 = 1 };
 
-// Instruction descriptor: D = f32, A/B format, operand majors (0 = K-major, 1 = MN-major), N, M.
-__host__ __device__ constexpr uint32_t MakeInstrDesc(uint32_t fmt, uint32_t a_mn_major, uint32_t b_mn_major,
-                                                     uint32_t m, uint32_t n) {
-    return (1u << 4) | (fmt << 7) | (fmt << 10) | (a_mn_major << 15) | (b_mn_major << 16) | ((n >> 3) << 17) |
+// Instruction descriptor: D = f32, A and B formats (each f16 or bf16, independently), operand majors
+// (0 = K-major, 1 = MN-major), N, M.
+__host__ __device__ constexpr uint32_t MakeInstrDesc(uint32_t a_fmt, uint32_t b_fmt, uint32_t a_mn_major,
+                                                     uint32_t b_mn_major, uint32_t m, uint32_t n) {
+    return (1u << 4) | (a_fmt << 7) | (b_fmt << 10) | (a_mn_major << 15) | (b_mn_major << 16) | ((n >> 3) << 17) |
            ((m >> 4) << 24);
 }
 

@@ -67,6 +67,14 @@ def check_close(got_f32, expect64, dt, tag=""):
     if dt != ol.DT_F32 and denom > 0:
         floor = float(np.sqrt(((round_like(expect64, dt) - expect64) ** 2).sum())) / denom
     assert max_abs <= MAX_ABS[dt], f"max_abs={max_abs:.3e} > {MAX_ABS[dt]:.1e} {tag}"
-    budget = REL_L2 + (floor if dt == ol.DT_BF16 else 0.0)
+    # The 1e-3 bound is on the value BEFORE the final store. A correctly rounded bf16 result alone is 1.7e-3 away
+    # from the FP64 one on unit-variance data, and that rounding error is independent of the error made before the
+    # store, so the two add in quadrature: rel^2 <= floor^2 + (1e-3)^2. (fp16's floor, 2e-4, hardly matters.)
+    budget = float(np.sqrt(REL_L2 ** 2 + floor ** 2))
     assert rel <= budget, f"rel_l2={rel:.3e} > {budget:.3e} (rounding floor {floor:.3e}) {tag}"
     return max_abs, rel
+
+
+def error_before_store(rel, floor):
+    """Relative L2 error of the value before its final rounding, from the measured total and the rounding floor."""
+    return float(np.sqrt(max(rel * rel - floor * floor, 0.0)))
