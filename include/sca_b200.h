@@ -209,6 +209,35 @@ typedef struct ScaFlashVarlenParams {
 SCA_ABI long long sca_flash_varlen_workspace_bytes(int64_t num_seqs, int64_t total_q);
 SCA_ABI int sca_launch_flash_varlen(const ScaFlashVarlenParams* params, void* stream);
 
+/* Chunked prefill over a paged KV cache in one launch (no counterpart in the reference, which lists it as the step
+ * after the packed variable-length prefill: docs/flash_attention.md:95). A batch of sequences, each with S_q new
+ * query tokens and S_kv >= S_q tokens already in the cache (the new ones included, appended beforehand):
+ *   q / out  packed [total_q, num_heads, head_dim];  cu_seqlens_q: HOST int32 [num_seqs + 1]
+ *   k_pool / v_pool  one layer of the pool, [num_blocks, block_size, num_kv_heads, head_dim]
+ *   page_table  DEVICE int32 [num_seqs, max_blocks_per_seq]; seq_lens_kv: HOST int32 [num_seqs] = S_kv per sequence
+ * Keys are fetched page by page (one TMA box per page, block_size in {8, 16, 32, 64}); an entry < 0 or >= num_blocks
+ * contributes weight 0, as in the decode kernel (src/backends/paged/page_table.cuh:18-36). The causal mask is
+ * bottom-right aligned per sequence: query i of S_q sees keys j <= i + (S_kv - S_q).
+ * `workspace`: device memory of sca_flash_varlen_workspace_bytes(num_seqs, total_q) bytes, untouched until the launch
+ * has finished. */
+typedef struct ScaFlashPagedParams {
+    const void* q;
+    void* out;
+    const void* k_pool;
+    const void* v_pool;
+    const int32_t* page_table;
+    int64_t total_q, num_heads, num_kv_heads, head_dim, num_seqs;
+    int64_t num_blocks, block_size, max_blocks_per_seq;
+    const int32_t* cu_seqlens_q;
+    const int32_t* seq_lens_kv;
+    float scale;
+    int32_t causal;
+    int32_t dtype_id;
+    void* workspace;
+    int64_t workspace_bytes;
+} ScaFlashPagedParams;
+SCA_ABI int sca_launch_flash_paged(const ScaFlashPagedParams* params, void* stream);
+
 /* Sequence-split decode without a library collective (no counterpart in the reference).
  *
  * Every rank creates one exchange buffer (sca_peer_buffer_bytes / _create), hands its 64-byte handle to

@@ -24,7 +24,7 @@ EXPORTED_SYMBOLS = [
     "sca_launch_kv_gather", "sca_launch_kv_append_batched", "sca_launch_decode_partials",
     "sca_peer_buffer_bytes", "sca_peer_buffer_create", "sca_peer_buffer_open", "sca_peer_buffer_close",
     "sca_peer_buffer_destroy", "sca_peer_exchange_status", "sca_launch_seqsplit_exchange",
-    "sca_flash_varlen_workspace_bytes", "sca_launch_flash_varlen",
+    "sca_flash_varlen_workspace_bytes", "sca_launch_flash_varlen", "sca_launch_flash_paged",
 ]
 
 PEER_MAX_RANKS = 16
@@ -97,6 +97,15 @@ class FlashVarlenParams(C.Structure):
         ("dtype_id", C.c_int32), ("workspace", C.c_void_p), ("workspace_bytes", C.c_int64)]
 
 
+class FlashPagedParams(C.Structure):
+    _fields_ = [("q", C.c_void_p), ("out", C.c_void_p), ("k_pool", C.c_void_p), ("v_pool", C.c_void_p),
+                ("page_table", C.c_void_p)] + [
+        (n, C.c_int64) for n in ("total_q", "num_heads", "num_kv_heads", "head_dim", "num_seqs", "num_blocks", "block_size",
+                                 "max_blocks_per_seq")] + [
+        ("cu_seqlens_q", C.c_void_p), ("seq_lens_kv", C.c_void_p), ("scale", C.c_float), ("causal", C.c_int32),
+        ("dtype_id", C.c_int32), ("workspace", C.c_void_p), ("workspace_bytes", C.c_int64)]
+
+
 class SeqSplitExchange(C.Structure):
     _fields_ = [("peer_buffers", C.c_void_p * PEER_MAX_RANKS), ("rank", C.c_int32), ("world", C.c_int32),
                 ("rows", C.c_int64), ("head_dim", C.c_int64), ("num_splits", C.c_int64), ("epoch", C.c_uint32),
@@ -149,6 +158,7 @@ def lib() -> C.CDLL:
     l.sca_flash_varlen_workspace_bytes.argtypes = [C.c_int64, C.c_int64]
     l.sca_flash_varlen_workspace_bytes.restype = C.c_longlong
     l.sca_launch_flash_varlen.argtypes = [C.POINTER(FlashVarlenParams), C.c_void_p]
+    l.sca_launch_flash_paged.argtypes = [C.POINTER(FlashPagedParams), C.c_void_p]
     l.sca_launch_decode_partials.argtypes = [C.POINTER(DecodeFwdParams), C.c_void_p]
     l.sca_peer_buffer_bytes.argtypes = [C.c_int32, C.c_int64, C.c_int64]
     l.sca_peer_buffer_bytes.restype = C.c_longlong

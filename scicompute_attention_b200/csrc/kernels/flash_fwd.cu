@@ -109,7 +109,7 @@ struct FlashGeom {
     static constexpr int kQTileBytes = kKBlocks * kQBlockBytes;
     static constexpr int kKvTileBytes = kKBlocks * kKvBlockBytes;
     static constexpr int kSlots = (DP == 64) ? 8 : 5;  // K/V ring
-    static constexpr int kBarrierBytes = 256;
+    static constexpr int kBarrierBytes = 384;
     static constexpr int kSmemBytes = 1024 + QT * kQTileBytes + kSlots * kKvTileBytes + kBarrierBytes;
     static constexpr int kSCol = 0;                         // S_t at kSCol + t * 128
     static constexpr int kOCol = 256;                       // O_t at kOCol + t * DP
@@ -133,6 +133,11 @@ struct FlashKernelParams {
     const int4* seqs;
     const int2* entries;
     int num_entries;
+    // paged K/V (kPaged kernels): the K/V tensor maps cover one layer's pool viewed as [blocks * block_size, H_kv, D]
+    // with a box of block_size rows; a KV tile is assembled page by page through the sequence's page-table row
+    const int32_t* page_table;   // device [num_seqs, max_blocks_per_seq], -1 = unmapped
+    int max_blocks_per_seq, num_kv_blocks;
+    int block_size, block_shift;  // block_size = 1 << block_shift
 };
 
 // KV tiles a query tile starting at row m0 of its sequence has to visit.
@@ -147,7 +152,8 @@ __device__ __forceinline__ int TilesFor(int m0, int seq_q, int seq_kv, int causa
 
 // kVarlen: the work list comes from the (sequence, query block) table of a packed ragged batch; otherwise it is
 // computed from the dense [B, H, S, D] geometry and every per-sequence quantity is a launch constant.
-template <typename T, int DP, int QT, int BN, bool kVarlen>
+// kPaged (only with kVarlen): K and V of a sequence are scattered over the pages of a KV pool.
+template <typename T, int DP, int QT, int BN, bool kVarlen, bool kPaged = false>
 __global__ void __launch_bounds__(kFlashThreads, 1)
 flash_fwd_sm100_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
                        const __grid_constant__ CUtensorMap map_v, const FlashKernelParams p) {
@@ -169,12 +175,23 @@ flash_fwd_sm100_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
     constexpr int kODone = kPFull + 2;              // [2]
     constexpr int kQEmpty = kODone + 2;             // [2]
     constexpr int kOFree = kQEmpty + 2;             // [2]
-    constexpr int kNumBars = kOFree + 2;
+    constexpr int kVReady = kOFree + 2;             // [kSlots] paged bf16: V tile rewritten as fp16 in place
+    constexpr int kNumBars = kVReady + G::kSlots;
+    // P and V enter the P V product as fp16 also for bf16 inputs (PvFormat). Contiguous V comes from an fp16 copy made
+    // before the launch; the pages of a pool are rewritten tile by tile in shared memory by warps 2 and 3 instead
+    // (a copy of the pool would cost more than the prefill), at the price of some issue slots of two schedulers.
     using PT = typename PvFormat<T>::type;
-    constexpr bool kCvtV = PvFormat<T>::kConvertV;
+    constexpr bool kCvtInKernel = kPaged && PvFormat<T>::kConvertV;
+    constexpr int kConverterThreads = 64;
+    static_assert(!kPaged || kVarlen, "paged K/V runs on the packed work list");
     static_assert(kNumBars * 8 + 16 <= G::kBarrierBytes, "barrier area too small");
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(smem + (bar_base - smem_base) + kNumBars * 8);
     volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+    // paged K/V: which pages of a KV tile are mapped (bit i = i-th page of the tile), written by the producer when
+    // it loads the K tile and read by the softmax groups; indexed by the CTA's running KV-tile count
+    constexpr int kValidRing = 16;
+    volatile uint32_t* valid_ring = reinterpret_cast<volatile uint32_t*>(tmem_slot + 2);
+    static_assert(kNumBars * 8 + 8 + kValidRing * 4 <= G::kBarrierBytes, "barrier area too small");
 
     // One query tile per CTA (head dims above 128): no second tile to ping-pong with, so the scores are double-
     // buffered instead: S(j+1) is computed while the softmax of block j runs. The barriers s_full / p_full / o_done
@@ -191,6 +208,7 @@ flash_fwd_sm100_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
     const int total_items = kVarlen ? p.num_entries * p.heads : p.m_blocks * bh_count;
     struct Item {
         int b, h, h_kv;
+        int seq;                      // index of the sequence (row of the page table); 0 for dense problems
         int q_tok0, kv_tok0;          // first row of the sequence in the packed tensors (0 for dense problems)
         int seq_q, seq_kv, diagonal;  // of this item's sequence
         int m0[2];                    // first query row of each tile, relative to the sequence
@@ -204,6 +222,7 @@ flash_fwd_sm100_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
             const int2 entry = __ldg(p.entries + idx / p.heads);
             const int4 seq = __ldg(p.seqs + entry.x);
             mb = entry.y;
+            w.seq = entry.x;
             w.b = 0;
             w.h = idx % p.heads;
             w.q_tok0 = seq.x;
@@ -213,6 +232,7 @@ flash_fwd_sm100_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
             w.diagonal = p.causal ? seq.w - seq.z : 0;  // bottom-right aligned mask
         } else {
             mb = p.m_blocks - 1 - idx / bh_count;
+            w.seq = 0;
             const int bh = idx % bh_count;
             w.b = bh / p.heads;
             w.h = bh % p.heads;
@@ -249,6 +269,7 @@ flash_fwd_sm100_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
         for (int i = 0; i < G::kSlots; ++i) {
             MbarInit(bar(kKvFull + i), 1);
             MbarInit(bar(kKvEmpty + i), 1);
+            MbarInit(bar(kVReady + i), kConverterThreads);
         }
         *abort_flag = 0;
         FenceBarrierInit();
@@ -264,7 +285,97 @@ flash_fwd_sm100_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
 
     bool failed = false;
 
-    if (warp == 0) {
+    if (warp == 0 && kPaged) {
+        // ================================ TMA producer, paged K/V ===================================
+        // The whole warp walks the work list: the lanes fetch the page ids of a tile together (one coalesced read
+        // of the table row), lane 0 waits for the ring slot and issues one box load per page and column block. A
+        // page that is unmapped (entry < 0 or >= num_kv_blocks) is loaded from beyond the pool, i.e. zero-filled,
+        // and its columns are masked in the softmax through valid_ring.
+        if (lane == 0) {
+            PrefetchTensorMap(&map_q);
+            PrefetchTensorMap(&map_k);
+            PrefetchTensorMap(&map_v);
+        }
+        uint32_t q_uses[2] = {0, 0};
+        uint32_t kv_loads = 0;
+        uint32_t tiles_before = 0;  // KV tiles of the items this CTA has finished
+        const int pages_per_tile = BN >> p.block_shift;
+        const int page_bytes = p.block_size * 128;  // one page inside one 64-element column block
+        bool ok = true;
+        for (int r = 0; r < rounds && ok; ++r) {
+            const int idx = item_of_round(r);
+            if (idx < 0) continue;
+            const Item w = decode_item(idx);
+            if (lane == 0) {
+                for (int t = 0; t < QT && ok; ++t) {
+                    if (w.ntiles[t] == 0) continue;
+                    if (q_uses[t] > 0) ok = MbarWait(bar(kQEmpty + t), (q_uses[t] - 1) & 1u, abort_flag);
+                    if (!ok) break;
+                    MbarExpectTx(bar(kQFull + t), G::kQTileBytes);
+                    for (int kb = 0; kb < G::kKBlocks; ++kb) {
+                        TmaLoad4D(q_smem + t * G::kQTileBytes + kb * G::kQBlockBytes, &map_q, bar(kQFull + t), kb * 64,
+                                  w.q_tok0 + w.m0[t], w.h, w.b);
+                    }
+                    ++q_uses[t];
+                }
+            }
+            ok = __shfl_sync(0xffffffffu, ok ? 1 : 0, 0) != 0;
+            const int32_t* row = p.page_table + static_cast<int64_t>(w.seq) * p.max_blocks_per_seq;
+            for (int it = 0; it < 2 * w.n_max && ok; ++it, ++kv_loads) {
+                bool is_v;
+                int tile;
+                if (kDoubleS) {
+                    const int n = w.n_max;
+                    const int lead = n > 1 ? 2 : 1;
+                    if (it < lead) {
+                        is_v = false;
+                        tile = it;
+                    } else {
+                        const int f = it - lead, kk = n - lead;
+                        is_v = f >= 2 * kk || (f & 1) == 0;
+                        tile = f < 2 * kk ? (is_v ? (f >> 1) : (f >> 1) + 2) : kk + (f - 2 * kk);
+                    }
+                } else {
+                    is_v = (it & 1) != 0;
+                    tile = it >> 1;
+                }
+                // page ids of this tile, one per lane
+                const int logical = tile * pages_per_tile + lane;
+                int32_t phys = -1;
+                if (lane < pages_per_tile && logical < p.max_blocks_per_seq &&
+                    (static_cast<int64_t>(logical) << p.block_shift) < w.seq_kv) {
+                    phys = __ldg(row + logical);
+                }
+                const bool mapped = phys >= 0 && phys < p.num_kv_blocks;
+                const uint32_t valid = __ballot_sync(0xffffffffu, mapped);
+                const uint32_t slot = kv_loads % G::kSlots;
+                const uint32_t phase = (kv_loads / G::kSlots) & 1u;
+                if (lane == 0) {
+                    ok = MbarWait(bar(kKvEmpty + slot), phase ^ 1u, abort_flag);
+                    if (ok) {
+                        if (!is_v) valid_ring[(tiles_before + tile) % kValidRing] = valid;
+                        MbarExpectTx(bar(kKvFull + slot), G::kKvTileBytes);
+                    }
+                }
+                ok = __shfl_sync(0xffffffffu, ok ? 1 : 0, 0) != 0;
+                if (!ok) break;
+                const CUtensorMap* map = is_v ? &map_v : &map_k;
+                for (int pg = 0; pg < pages_per_tile; ++pg) {
+                    const int32_t id = __shfl_sync(0xffffffffu, phys, pg);
+                    // an unmapped page reads from the first row behind the pool: all zeros
+                    const int first_row = ((valid >> pg) & 1u) ? (id << p.block_shift) : (p.num_kv_blocks << p.block_shift);
+                    if (lane == 0) {
+                        for (int kb = 0; kb < G::kKBlocks; ++kb) {
+                            TmaLoad4D(ring_smem + slot * G::kKvTileBytes + kb * G::kKvBlockBytes + pg * page_bytes, map,
+                                      bar(kKvFull + slot), kb * 64, first_row, w.h_kv, 0);
+                        }
+                    }
+                }
+            }
+            tiles_before += static_cast<uint32_t>(w.n_max);
+        }
+        failed = !ok;
+    } else if (warp == 0) {
         // ================================ TMA producer =============================================
         if (lane == 0) {
             PrefetchTensorMap(&map_q);
@@ -330,7 +441,7 @@ flash_fwd_sm100_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
             constexpr uint32_t idesc_s = MakeInstrDesc(fmt, fmt, 0, 0, kBlockM, BN);  // Q K^T: both K-major
             // P V: V is MN-major; both operands in the P V format (fp16 also for bf16 inputs, see PvFormat: V then
             // comes from the fp16 copy map_v points at)
-            constexpr uint32_t fmt_pv = kCvtV ? kFmtF16 : fmt;
+            constexpr uint32_t fmt_pv = PvFormat<T>::kConvertV ? kFmtF16 : fmt;
             constexpr uint32_t idesc_o = MakeInstrDesc(fmt_pv, fmt_pv, 0, 1, kBlockM, DP);
             // Descriptors are built once and advanced by compile-time constants, so that issuing one
             // tcgen05.mma costs a handful of instructions (this thread alone has to keep the tensor pipe fed).
@@ -366,15 +477,17 @@ flash_fwd_sm100_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
             uint32_t q_uses[2] = {0, 0};    // items finished per query buffer
             uint32_t steps[2] = {0, 0};     // KV tiles processed per query tile (phase of s_full / p_full / o_done)
             uint32_t kv_base = 0;           // ring position of this item's K_0
+            uint32_t v_uses[G::kSlots] = {};  // V tiles consumed per ring slot (phase of v_ready)
             bool ok = true;
             if constexpr (kDoubleS) {
                 // single query tile, two score buffers: S(0), S(1), then P(j) V_j followed by S(j+2) into the buffer
                 // P(j) came from (same in-order stream, so the overwrite happens after the read)
                 uint32_t buf_uses[2] = {0, 0};  // P tiles consumed per score buffer (phase of p_full)
-                auto next_slot = [&](uint32_t* slot) {
+                auto next_slot = [&](uint32_t* slot, bool is_v) {
                     *slot = kv_base % G::kSlots;
                     const uint32_t phase = (kv_base / G::kSlots) & 1u;
                     ++kv_base;
+                    if (kCvtInKernel && is_v) return MbarWait(bar(kVReady + *slot), v_uses[*slot]++ & 1u, abort_flag);
                     return MbarWait(bar(kKvFull + *slot), phase, abort_flag);
                 };
                 for (int r = 0; r < rounds && ok; ++r) {
@@ -386,7 +499,7 @@ flash_fwd_sm100_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
                     ok = MbarWait(bar(kQFull), q_uses[0] & 1u, abort_flag);
                     uint32_t slot = 0;
                     for (int i = 0; i < 2 && i < n && ok; ++i) {
-                        ok = next_slot(&slot);
+                        ok = next_slot(&slot, false);
                         if (!ok) break;
                         TcFenceAfter();
                         s_tmem_db = tmem_base + G::kSCol + i * 64;
@@ -400,7 +513,7 @@ flash_fwd_sm100_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
                         ok = MbarWait(bar(kPFull + buf), buf_uses[buf] & 1u, abort_flag);
                         ++buf_uses[buf];
                         if (ok && j == 0 && q_uses[0] > 0) ok = MbarWait(bar(kOFree), (q_uses[0] - 1) & 1u, abort_flag);
-                        if (ok) ok = next_slot(&slot);  // V_j
+                        if (ok) ok = next_slot(&slot, true);  // V_j
                         if (!ok) break;
                         TcFenceAfter();
                         s_tmem_db = tmem_base + G::kSCol + buf * 64;
@@ -408,7 +521,7 @@ flash_fwd_sm100_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
                         MmaCommit(bar(kODone + buf));
                         MmaCommit(bar(kKvEmpty + slot));
                         if (j + 2 < n) {
-                            ok = next_slot(&slot);  // K_j+2
+                            ok = next_slot(&slot, false);  // K_j+2
                             if (!ok) break;
                             TcFenceAfter();
                             issue_s(0, slot);
@@ -445,7 +558,8 @@ flash_fwd_sm100_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
                 for (int j = 0; j < w.n_max && ok; ++j) {
                     const int it_v = 2 * j + 1;
                     const int it_k = 2 * j + 2;
-                    ok = MbarWait(bar(kKvFull + slot_of(it_v)), phase_of(it_v), abort_flag);
+                    if (kCvtInKernel) ok = MbarWait(bar(kVReady + slot_of(it_v)), v_uses[slot_of(it_v)]++ & 1u, abort_flag);
+                    else ok = MbarWait(bar(kKvFull + slot_of(it_v)), phase_of(it_v), abort_flag);
                     if (ok && j + 1 < w.n_max) ok = MbarWait(bar(kKvFull + slot_of(it_k)), phase_of(it_k), abort_flag);
                     if (!ok) break;
                     for (int t = 0; t < QT; ++t) {
@@ -475,6 +589,54 @@ flash_fwd_sm100_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
             }
             failed = !ok;
         }
+    } else if (kCvtInKernel && warp < 4) {
+        // ================================ V converter (warps 2 and 3, paged bf16) ====================
+        // Walks the ring in the producer's order; every V tile is rewritten in place from bf16 to fp16 once its
+        // bytes have landed, then handed to the MMA thread through v_ready. K tiles are not touched.
+        const int tid = threadIdx.x - 64;
+        uint32_t kv_loads = 0;
+        bool ok = true;
+        for (int r = 0; r < rounds && ok; ++r) {
+            const int idx = item_of_round(r);
+            if (idx < 0) continue;
+            const Item w = decode_item(idx);
+            for (int it = 0; it < 2 * w.n_max && ok; ++it, ++kv_loads) {
+                bool is_v;
+                if (kDoubleS) {
+                    const int n = w.n_max;
+                    const int lead = n > 1 ? 2 : 1;
+                    if (it < lead) {
+                        is_v = false;
+                    } else {
+                        const int f = it - lead, kk = n - lead;
+                        is_v = f >= 2 * kk || (f & 1) == 0;
+                    }
+                } else {
+                    is_v = (it & 1) != 0;
+                }
+                if (!is_v) continue;
+                const uint32_t slot = kv_loads % G::kSlots;
+                const uint32_t phase = (kv_loads / G::kSlots) & 1u;
+                ok = __all_sync(0xffffffffu, MbarWait(bar(kKvFull + slot), phase, abort_flag));
+                if (!ok) break;
+                uint4* tile = reinterpret_cast<uint4*>(smem + (ring_smem - smem_base) + slot * G::kKvTileBytes);
+#pragma unroll 4
+                for (int c = tid; c < G::kKvTileBytes / 16; c += kConverterThreads) {
+                    uint4 x = tile[c];
+                    uint32_t* word = reinterpret_cast<uint32_t*>(&x);
+#pragma unroll
+                    for (int e = 0; e < 4; ++e) {
+                        const float2 f = Unpack2<__nv_bfloat16>(word[e]);
+                        // one instruction for both lanes; values beyond the fp16 range saturate instead of becoming inf
+                        asm("cvt.rn.satfinite.f16x2.f32 %0, %1, %2;" : "=r"(word[e]) : "f"(f.y), "f"(f.x));
+                    }
+                    tile[c] = x;
+                }
+                FenceProxyAsync();  // generic-proxy writes -> visible to the tensor core's reads
+                MbarArrive(bar(kVReady + slot));
+            }
+        }
+        failed = !ok;
     } else if (warp >= 4) {
         // ================================ softmax groups ============================================
         const int t = (warp - 4) >> 2;
@@ -485,6 +647,8 @@ flash_fwd_sm100_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
         const uint32_t o_addr = tmem_base + lane_bits + G::kOCol + t * DP;
         uint32_t steps = 0;  // KV tiles this group has processed (phase of s_full / p_full / o_done)
         uint32_t buf_steps0 = 0, buf_steps1 = 0;  // double-buffered scores: tiles taken from each buffer
+        uint32_t tiles_before = 0;  // paged K/V: KV tiles of the items this CTA has finished (index into valid_ring)
+        const uint32_t all_pages = kPaged ? ((BN >> p.block_shift) >= 32 ? 0xffffffffu : (1u << (BN >> p.block_shift)) - 1u) : 0u;
         bool ok = true;
 
         for (int r = 0; r < rounds && ok && t < QT; ++r) {
@@ -492,6 +656,8 @@ flash_fwd_sm100_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
             if (idx < 0) continue;
             const Item w = decode_item(idx);
             const int n_t = w.ntiles[t];
+            const uint32_t tiles_base = tiles_before;
+            tiles_before += static_cast<uint32_t>(w.n_max);
             if (n_t == 0) continue;
             const int row = w.m0[t] + row_in_tile;
             float m_ref = -CUDART_INF_F;  // reference point of the exponentials (log2 domain)
@@ -522,7 +688,9 @@ flash_fwd_sm100_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
                 const int kv_limit = w.seq_kv - col0;                                   // columns >= kv_limit do not exist
                 const int causal_limit = p.causal ? (row + w.diagonal - col0 + 1) : BN;  // columns >= limit are masked
                 const int limit = min(kv_limit, causal_limit);
-                const bool ragged = limit < BN;
+                const uint32_t pages = kPaged ? valid_ring[(tiles_base + j) % kValidRing] : 0u;
+                const bool holes = kPaged && pages != all_pages;   // some page of this tile is unmapped
+                const bool ragged = limit < BN || holes;
                 float part4[4] = {0.0f, 0.0f, 0.0f, 0.0f};  // this step's share of the row sum
     #pragma unroll
                 for (int half = 0; half < BN / 64; ++half) {
@@ -533,8 +701,11 @@ flash_fwd_sm100_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
                     if (ragged) {
     #pragma unroll
                         for (int i = 0; i < 32; ++i) {
-                            if (half * 64 + i >= limit) ra[i] = 0xff800000u;       // -inf
-                            if (half * 64 + 32 + i >= limit) rb[i] = 0xff800000u;
+                            const int ca = half * 64 + i, cb = half * 64 + 32 + i;
+                            const bool gone_a = kPaged && holes && !((pages >> (ca >> p.block_shift)) & 1u);
+                            const bool gone_b = kPaged && holes && !((pages >> (cb >> p.block_shift)) & 1u);
+                            if (ca >= limit || gone_a) ra[i] = 0xff800000u;       // -inf
+                            if (cb >= limit || gone_b) rb[i] = 0xff800000u;
                         }
                     }
                     float mx4[4] = {-CUDART_INF_F, -CUDART_INF_F, -CUDART_INF_F, -CUDART_INF_F};
@@ -862,11 +1033,27 @@ int UploadVarlenWork(const VarlenWork& vw, int rows_per_entry, int block_n, bool
     return SCA_OK;
 }
 
+// A paged KV pool behind a packed batch: f.k / f.v point at one layer's pool [num_blocks, block_size, H_kv, D].
+struct PagedWork {
+    const int32_t* page_table;
+    int64_t num_blocks, block_size, max_blocks_per_seq;
+};
+
 template <typename T, int DP, int QT, int BN>
-int LaunchFlash(const ScaFlashFwdParams& f, cudaStream_t stream, const VarlenWork* varlen = nullptr) {
+int LaunchFlash(const ScaFlashFwdParams& f, cudaStream_t stream, const VarlenWork* varlen = nullptr,
+                const PagedWork* paged = nullptr) {
     using G = FlashGeom<DP, QT, BN>;
     CUtensorMap map_q, map_k, map_v;
     if (int rc = MakeMap(&map_q, f.q, f.dtype_id, f.head_dim, f.seq_q, f.num_heads, f.batch, f.q_ss, f.q_sh, f.q_sb, kBlockM, "q")) return rc;
+    if (paged != nullptr) {
+        // the pool as [rows = blocks * block_size, H_kv, D]; one box = one page of one kv head and column block
+        const int64_t rows = paged->num_blocks * paged->block_size;
+        const int64_t row_elems = f.num_kv_heads * f.head_dim;
+        if (int rc = MakeMap(&map_k, f.k, f.dtype_id, f.head_dim, rows, f.num_kv_heads, 1, row_elems, f.head_dim, rows * row_elems,
+                             static_cast<int>(paged->block_size), "k pool")) return rc;
+        if (int rc = MakeMap(&map_v, f.v, f.dtype_id, f.head_dim, rows, f.num_kv_heads, 1, row_elems, f.head_dim, rows * row_elems,
+                             static_cast<int>(paged->block_size), "v pool")) return rc;
+    } else
     if (int rc = MakeMap(&map_k, f.k, f.dtype_id, f.head_dim, f.seq_kv, f.num_kv_heads, f.batch, f.k_ss, f.k_sh, f.k_sb, BN, "k")) return rc;
     // bf16: V goes through an fp16 copy (PvFormat). The copy is a stream-ordered temporary, released behind the launch.
     struct Temporary {
@@ -876,7 +1063,9 @@ int LaunchFlash(const ScaFlashFwdParams& f, cudaStream_t stream, const VarlenWor
             if (ptr != nullptr && cudaFreeAsync(ptr, stream) != cudaSuccess) cudaGetLastError();
         }
     } v16;
-    if (PvFormat<T>::kConvertV) {
+    if (paged != nullptr) {
+        // map_v is set above: the pool is read in place, in the input format
+    } else if (PvFormat<T>::kConvertV) {
         if (!Aligned16(f.v) || f.v_sb % 8 != 0 || f.v_sh % 8 != 0 || f.v_ss % 8 != 0 || f.head_dim % 8 != 0) {
             return Fail(SCA_INVALID_ARGUMENT, "flash attention: v must be 16-byte aligned with strides that are multiples of 8 elements");
         }
@@ -927,7 +1116,17 @@ int LaunchFlash(const ScaFlashFwdParams& f, cudaStream_t stream, const VarlenWor
         return Fail(SCA_INVALID_ARGUMENT, "flash attention: grid of " + std::to_string(ctas) + " blocks is out of range");
     }
     const unsigned grid = static_cast<unsigned>(std::min<int64_t>(ctas, SmCount()));  // one persistent CTA per SM
-    if (varlen != nullptr) {
+    if (paged != nullptr) {
+        p.page_table = paged->page_table;
+        p.max_blocks_per_seq = static_cast<int>(paged->max_blocks_per_seq);
+        p.num_kv_blocks = static_cast<int>(paged->num_blocks);
+        p.block_size = static_cast<int>(paged->block_size);
+        p.block_shift = 0;
+        while ((1 << p.block_shift) < p.block_size) ++p.block_shift;
+        const void* fn = reinterpret_cast<const void*>(&flash_fwd_sm100_kernel<T, DP, QT, BN, true, true>);
+        if (int rc = EnsureDynamicSmem(fn, G::kSmemBytes, "flash_fwd_sm100_kernel")) return rc;
+        flash_fwd_sm100_kernel<T, DP, QT, BN, true, true><<<grid, kFlashThreads, G::kSmemBytes, stream>>>(map_q, map_k, map_v, p);
+    } else if (varlen != nullptr) {
         const void* fn = reinterpret_cast<const void*>(&flash_fwd_sm100_kernel<T, DP, QT, BN, true>);
         if (int rc = EnsureDynamicSmem(fn, G::kSmemBytes, "flash_fwd_sm100_kernel")) return rc;
         flash_fwd_sm100_kernel<T, DP, QT, BN, true><<<grid, kFlashThreads, G::kSmemBytes, stream>>>(map_q, map_k, map_v, p);
@@ -974,17 +1173,18 @@ int ValidateFlash(const ScaFlashFwdParams* params) {
 }
 
 template <typename T>
-int LaunchFlashTyped(const ScaFlashFwdParams& f, cudaStream_t stream, const VarlenWork* varlen = nullptr) {
+int LaunchFlashTyped(const ScaFlashFwdParams& f, cudaStream_t stream, const VarlenWork* varlen = nullptr,
+                     const PagedWork* paged = nullptr) {
     // head dims that are not a multiple of 64 run on the next padded geometry: the TMA unit
     // zero-fills the missing columns of Q, K and V, which leaves S and the real columns of O unchanged
     switch (f.head_dim) {
         case 32:
-        case 64: return LaunchFlash<T, 64, 2, 128>(f, stream, varlen);
+        case 64: return LaunchFlash<T, 64, 2, 128>(f, stream, varlen, paged);
         case 96:
-        case 128: return LaunchFlash<T, 128, 2, 128>(f, stream, varlen);
+        case 128: return LaunchFlash<T, 128, 2, 128>(f, stream, varlen, paged);
         case 160:
         case 192:
-        case 256: return LaunchFlash<T, 256, 1, 64>(f, stream, varlen);
+        case 256: return LaunchFlash<T, 256, 1, 64>(f, stream, varlen, paged);
         default: break;
     }
     return Fail(SCA_INVALID_ARGUMENT, "flash attention: head_dim=" + std::to_string(f.head_dim) + " is not instantiated");
@@ -1072,4 +1272,69 @@ extern "C" int sca_launch_flash_varlen(const ScaFlashVarlenParams* params, void*
     cudaStream_t s = static_cast<cudaStream_t>(stream);
     return f.dtype_id == SCA_DTYPE_F16 ? LaunchFlashTyped<__half>(f, s, &vw)
                                        : LaunchFlashTyped<__nv_bfloat16>(f, s, &vw);
+}
+
+extern "C" int sca_launch_flash_paged(const ScaFlashPagedParams* params, void* stream) {
+    ClearError();
+    if (params == nullptr || params->cu_seqlens_q == nullptr || params->seq_lens_kv == nullptr) {
+        return Fail(SCA_INVALID_ARGUMENT, "flash paged: null parameter block or host lengths");
+    }
+    const ScaFlashPagedParams& x = *params;
+    if (x.q == nullptr || x.out == nullptr || x.k_pool == nullptr || x.v_pool == nullptr || x.page_table == nullptr) {
+        return Fail(SCA_INVALID_ARGUMENT, "flash paged: null tensor pointer");
+    }
+    if (x.num_seqs < 1 || x.total_q < 1) return Fail(SCA_INVALID_ARGUMENT, "flash paged: empty batch");
+    if (x.cu_seqlens_q[0] != 0 || x.cu_seqlens_q[x.num_seqs] != x.total_q) {
+        return Fail(SCA_INVALID_ARGUMENT, "flash paged: query offsets must start at 0 and end at total_q");
+    }
+    if (x.block_size != 8 && x.block_size != 16 && x.block_size != 32 && x.block_size != 64) {
+        return Fail(SCA_INVALID_ARGUMENT, "flash paged: block_size=" + std::to_string(x.block_size) +
+                                              " (pages are loaded as boxes of 8, 16, 32 or 64 tokens)");
+    }
+    if (x.num_blocks < 1 || x.max_blocks_per_seq < 1 || x.num_blocks * x.block_size > 0x7fffff00LL) {
+        return Fail(SCA_INVALID_ARGUMENT, "flash paged: invalid pool geometry");
+    }
+    // kv offsets for the shared work-list builder: only the lengths are used on the device
+    std::vector<int32_t> cu_kv(static_cast<size_t>(x.num_seqs) + 1, 0);
+    for (int64_t s = 0; s < x.num_seqs; ++s) {
+        const int64_t have = x.seq_lens_kv[s];
+        if (have < 1 || have > x.max_blocks_per_seq * x.block_size) {
+            return Fail(SCA_INVALID_ARGUMENT, "flash paged: sequence " + std::to_string(s) + " has " + std::to_string(have) +
+                                                  " tokens in the cache (the page-table row holds " +
+                                                  std::to_string(x.max_blocks_per_seq * x.block_size) + ")");
+        }
+        const int64_t next = static_cast<int64_t>(cu_kv[static_cast<size_t>(s)]) + have;
+        if (next > 0x7fffffffLL) return Fail(SCA_INVALID_ARGUMENT, "flash paged: more than 2^31 cached tokens in one call");
+        cu_kv[static_cast<size_t>(s) + 1] = static_cast<int32_t>(next);
+    }
+    ScaFlashFwdParams f{};
+    f.q = x.q;
+    f.k = x.k_pool;
+    f.v = x.v_pool;
+    f.out = x.out;
+    f.batch = 1;
+    f.num_heads = x.num_heads;
+    f.num_kv_heads = x.num_kv_heads;
+    f.seq_q = x.total_q;
+    f.seq_kv = cu_kv.back();
+    f.head_dim = x.head_dim;
+    f.q_ss = x.num_heads * x.head_dim;
+    f.q_sh = x.head_dim;
+    f.q_sb = x.total_q * f.q_ss;
+    f.o_ss = f.q_ss;
+    f.o_sh = f.q_sh;
+    f.o_sb = f.q_sb;
+    f.scale = x.scale;
+    f.causal = x.causal;
+    f.dtype_id = x.dtype_id;
+    if (int rc = ValidateFlash(&f)) return rc;
+    VarlenWork vw{x.cu_seqlens_q, cu_kv.data(), x.num_seqs, x.workspace, x.workspace_bytes};
+    PagedWork pw{x.page_table, x.num_blocks, x.block_size, x.max_blocks_per_seq};
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    switch (f.dtype_id) {
+        case SCA_DTYPE_F16: return LaunchFlashTyped<__half>(f, s, &vw, &pw);
+        case SCA_DTYPE_BF16: return LaunchFlashTyped<__nv_bfloat16>(f, s, &vw, &pw);
+        default: break;
+    }
+    return Fail(SCA_INVALID_ARGUMENT, "flash paged: unsupported dtype id");
 }

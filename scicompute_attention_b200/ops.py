@@ -377,6 +377,45 @@ def flash_attention_varlen(q, k, v, cu_seqlens_q, cu_seqlens_kv, *, causal=False
     return out
 
 
+def flash_attention_paged(q, k_pool, v_pool, page_table, cu_seqlens_q, seq_lens_kv, *, causal=True, scale=None, stream=None):
+    """Chunked prefill over a paged KV cache in one launch: q packed [T_q, H_q, D] (the new tokens of every
+    sequence), pools [num_blocks, block_size, H_kv, D], page_table int32 [num_seqs, max_blocks_per_seq] on the device,
+    cu_seqlens_q (num_seqs + 1) and seq_lens_kv (num_seqs: tokens of each sequence in the cache, the new ones
+    included) on the HOST. Returns [T_q, H_q, D]."""
+    import numpy as np
+    _require_cuda(q, k_pool, v_pool, page_table)
+    if q.dim() != 3 or k_pool.dim() != 4 or tuple(k_pool.shape) != tuple(v_pool.shape) or not (
+            q.is_contiguous() and k_pool.is_contiguous() and v_pool.is_contiguous() and page_table.is_contiguous()):
+        raise _lib.ScaError(4, "paged prefill expects packed q [T, H, D] and contiguous pools [blocks, block_size, H_kv, D]")
+    if page_table.dtype != torch.int32 or page_table.dim() != 2:
+        raise _lib.ScaError(4, "page_table must be int32 [num_seqs, max_blocks_per_seq]")
+    cu_q = np.ascontiguousarray(cu_seqlens_q, dtype=np.int32)
+    lens = np.ascontiguousarray(seq_lens_kv, dtype=np.int32)
+    n = lens.shape[0]
+    if cu_q.ndim != 1 or cu_q.shape[0] != n + 1 or page_table.shape[0] < n:
+        raise _lib.ScaError(4, "cu_seqlens_q needs num_seqs + 1 entries, seq_lens_kv and the page table num_seqs")
+    tq, hq, d = q.shape
+    nblk, bs, hkv, dk = k_pool.shape
+    if dk != d:
+        raise _lib.ScaError(4, "pool head_dim differs from q")
+    out = torch.empty_like(q)
+    ws_bytes = lib().sca_flash_varlen_workspace_bytes(n, tq)
+    ws = torch.empty(max(int(ws_bytes), 16), dtype=torch.uint8, device=q.device)
+    p = _lib.FlashPagedParams()
+    p.q, p.out, p.k_pool, p.v_pool, p.page_table = q.data_ptr(), out.data_ptr(), k_pool.data_ptr(), v_pool.data_ptr(), page_table.data_ptr()
+    p.total_q, p.num_heads, p.num_kv_heads, p.head_dim, p.num_seqs = tq, hq, hkv, d, n
+    p.num_blocks, p.block_size, p.max_blocks_per_seq = nblk, bs, page_table.shape[1]
+    p.cu_seqlens_q, p.seq_lens_kv = cu_q.ctypes.data, lens.ctypes.data
+    p.scale = effective_scale(scale, d)
+    p.causal = 1 if causal else 0
+    p.dtype_id = dtype_id(q.dtype)
+    p.workspace, p.workspace_bytes = ws.data_ptr(), ws.numel()
+    check(lib().sca_launch_flash_paged(C.byref(p), _stream_ptr(stream)))
+    if stream is None:
+        ws.record_stream(torch.cuda.current_stream(q.device))
+    return out
+
+
 def simt_attention(q, k, v, *, causal=False, scale=None, return_lse=False, layout="bhsd", stream=None):
     """Functional SIMT attention behind the naive / tiled backends (any compute dtype)."""
     _require_cuda(q, k, v)

@@ -81,6 +81,27 @@ def test_c2_prefill_full_size(dtype_name):
     assert (out1.float() - 1.0).abs().max().item() <= H.MAX_ABS[_dt(dtype)]
 
 
+@pytest.mark.parametrize("dtype_name", ["bfloat16", "float16"])
+def test_c2_prefill_whole_output_against_the_oracle(dtype_name):
+    """Every element of the full C2 output (4 x 32 heads x 4096 causal rows) against the FP64 oracle on all host
+    threads - about half a minute of host work per dtype."""
+    import os
+
+    import torch
+    from scicompute_attention_b200 import ops
+    dtype = getattr(torch, dtype_name)
+    b, s = 4, 4096
+    q = _randn((b, HQ, s, D), 10, dtype)
+    k = _randn((b, HKV, s, D), 11, dtype)
+    v = _randn((b, HKV, s, D), 12, dtype)
+    out = ops.flash_attention(q, k, v, causal=True)
+    torch.cuda.synchronize()
+    threads = os.cpu_count() or 1
+    for bi in range(b):  # one batch element at a time keeps the FP64 copies small
+        expect = ol.attention_f64(_f32(q[bi:bi + 1]), _f32(k[bi:bi + 1]), _f32(v[bi:bi + 1]), causal=True, threads=threads)
+        H.check_close(_f32(out[bi:bi + 1]), expect, _dt(dtype), f"C2 whole output, batch {bi}, {dtype_name}")
+
+
 def test_c3_split_k_decode_full_size():
     import torch
     from scicompute_attention_b200 import ops
