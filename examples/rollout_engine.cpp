@@ -3,12 +3,18 @@
 // paged-attention call per layer and step). It plays the role of the reference's
 // examples/rollout_engine_stub.cpp (same stages: prefill on token-major views -> append -> page-table
 // sync -> paged decode), extended to several layers (one PagedKVCache per layer, because a cache
-// advances a sequence on every append) and to the batched append.
+// advances a sequence on every append), to the batched append, to follow-up prompts (a chunk of new tokens per
+// request that attends over the paged cache in ONE chunked-prefill launch per layer) and to several GPUs.
 //
-//   rollout_engine [--requests N] [--layers L] [--new-tokens T] [--prompt-min A] [--prompt-max B] [--verify]
+//   rollout_engine [--requests N] [--layers L] [--new-tokens T] [--prompt-min A] [--prompt-max B]
+//                  [--followup F] [--gpus G] [--verify]
 //
+// --gpus G serves G times the requests: the process starts one copy of itself per GPU (CUDA_VISIBLE_DEVICES = g),
+// every copy serves its own requests on its own caches - requests are independent, nothing crosses GPUs - and the
+// parent adds up the rates. --followup 0 skips the follow-up stage.
 // --verify re-computes the last decode step of layer 0 for every request with the split-K decode backend
-// on the request's gathered (contiguous) cache and fails if the two backends differ by more than 2e-3.
+// on the request's gathered (contiguous) cache, and the follow-up outputs of the first requests with the flash
+// backend on the gathered cache, and fails if the backends differ by more than 2e-3.
 // Exit codes: 0 ok, 2 no GPU, 3 KV budget, 4 a call failed, 5 verification failed.
 #include <algorithm>
 #include <chrono>
@@ -29,7 +35,8 @@ namespace {
 constexpr int64_t kHeadsQ = 32, kHeadsKv = 8, kHeadDim = 128, kBlockSize = 16;
 
 struct Args {
-    int64_t requests{32}, layers{4}, new_tokens{16}, prompt_min{64}, prompt_max{1024};
+    int64_t requests{32}, layers{4}, new_tokens{16}, prompt_min{64}, prompt_max{1024}, followup{64}, gpus{1};
+    int64_t shard{-1};  // >= 0: this process is copy `shard` of a multi-GPU run
     bool verify{false};
 };
 
@@ -47,6 +54,15 @@ bool Parse(int argc, char** argv, Args* a) {
         else if (s == "--new-tokens") ok = next(&a->new_tokens);
         else if (s == "--prompt-min") ok = next(&a->prompt_min);
         else if (s == "--prompt-max") ok = next(&a->prompt_max);
+        else if (s == "--gpus") ok = next(&a->gpus);
+        else if (s == "--followup") {
+            ok = i + 1 < argc;
+            if (ok) a->followup = std::atoll(argv[++i]);
+            ok = ok && a->followup >= 0;
+        } else if (s == "--shard") {
+            ok = i + 1 < argc;
+            if (ok) a->shard = std::atoll(argv[++i]);
+        }
         else if (s == "--verify") a->verify = true;
         else ok = false;
         if (!ok) {
@@ -101,11 +117,51 @@ double Ms(std::chrono::steady_clock::time_point a, std::chrono::steady_clock::ti
     return std::chrono::duration<double, std::milli>(b - a).count();
 }
 
+// One copy of this program per GPU; the parent adds up the "[rollout-rates]" lines of the copies.
+int RunOnSeveralGpus(const Args& args, const char* self) {
+    std::vector<FILE*> pipes;
+    for (int64_t g = 0; g < args.gpus; ++g) {
+        std::string cmd = "CUDA_VISIBLE_DEVICES=" + std::to_string(g) + " '" + self + "' --shard " + std::to_string(g) +
+                          " --requests " + std::to_string(args.requests) + " --layers " + std::to_string(args.layers) +
+                          " --new-tokens " + std::to_string(args.new_tokens) + " --prompt-min " + std::to_string(args.prompt_min) +
+                          " --prompt-max " + std::to_string(args.prompt_max) + " --followup " + std::to_string(args.followup) +
+                          (args.verify ? " --verify" : "") + " 2>&1";
+        FILE* f = popen(cmd.c_str(), "r");  // all copies run at the same time; they are read one after the other
+        if (f == nullptr) {
+            std::printf("[rollout] cannot start the copy for GPU %lld\n", static_cast<long long>(g));
+            return 4;
+        }
+        pipes.push_back(f);
+    }
+    double prefill = 0.0, decode = 0.0, followup = 0.0;
+    int worst = 0;
+    for (size_t g = 0; g < pipes.size(); ++g) {
+        char line[512];
+        while (std::fgets(line, sizeof(line), pipes[g]) != nullptr) {
+            double a = 0.0, b = 0.0, c = 0.0;
+            if (std::sscanf(line, "[rollout-rates] prefill=%lf decode=%lf followup=%lf", &a, &b, &c) == 3) {
+                prefill += a;
+                decode += b;
+                followup += c;
+            } else {
+                std::printf("[gpu %zu] %s", g, line);
+            }
+        }
+        const int status = pclose(pipes[g]);
+        const int code = (status >> 8) & 0xff;  // exit status of the shell = exit status of the copy
+        if (code != 0) worst = code;
+    }
+    std::printf("[rollout] %lld GPUs together: %.0f prompt tokens/s per layer, %.0f generated tokens/s, %.0f follow-up tokens/s per layer\n",
+                static_cast<long long>(args.gpus), prefill, decode, followup);
+    return worst;
+}
+
 }  // namespace
 
 int main(int argc, char** argv) {
     Args args;
     if (!Parse(argc, argv, &args)) return 1;
+    if (args.gpus > 1 && args.shard < 0) return RunOnSeveralGpus(args, argv[0]);
     std::shared_ptr<sci::Device> device = sci::DeviceManager::Instance().get_device(sci::DeviceType::kCUDA, 0);
     if (device == nullptr) {
         std::printf("[rollout] no CUDA device\n");
@@ -116,7 +172,7 @@ int main(int argc, char** argv) {
     for (int64_t r = 0; r < args.requests; ++r) {
         const int64_t span = args.prompt_max - args.prompt_min + 1;
         prompt[static_cast<size_t>(r)] = args.prompt_min + (r * 7919 + 13) % span;
-        tokens_needed += prompt[static_cast<size_t>(r)] + args.new_tokens;
+        tokens_needed += prompt[static_cast<size_t>(r)] + args.new_tokens + args.followup;
     }
 
     sca::KVCacheConfig kv_cfg;
@@ -158,7 +214,7 @@ int main(int argc, char** argv) {
     std::vector<sci::Tensor> q_in, k_in, v_in;
     for (int64_t r = 0; r < args.requests; ++r) {
         const int64_t n = prompt[static_cast<size_t>(r)];
-        const uint32_t seed = static_cast<uint32_t>(r * 131);
+        const uint32_t seed = static_cast<uint32_t>(r * 131 + (args.shard > 0 ? args.shard * 7717 : 0));
         q_in.push_back(Filled({n, kHeadsQ, kHeadDim}, *device, 1000 + seed, 1.0f));
         k_in.push_back(Filled({n, kHeadsKv, kHeadDim}, *device, 2000 + seed, 1.0f));
         v_in.push_back(Filled({n, kHeadsKv, kHeadDim}, *device, 3000 + seed, 0.5f));
@@ -234,6 +290,55 @@ int main(int argc, char** argv) {
     device->synchronize();
     const auto t2 = std::chrono::steady_clock::now();
 
+    std::vector<int64_t> decode_len(static_cast<size_t>(args.requests));  // cache lengths the last decode step saw
+    for (int64_t r = 0; r < args.requests; ++r) decode_len[static_cast<size_t>(r)] = caches[0].SeqLength(r);
+
+    // ---- follow-up prompts: a chunk of new tokens per request over the paged cache -----------------------
+    // The chunk's K/V go into the cache first (as for any prompt), then ONE chunked-prefill launch per layer serves
+    // all requests: every new token attends over its request's whole cached history, causally within the chunk.
+    double followup_ms = 0.0;
+    sci::Tensor followup_out;
+    std::vector<sci::Tensor> fq, fk, fv;
+    std::vector<int32_t> cu_follow(static_cast<size_t>(args.requests) + 1, 0);
+    if (args.followup > 0) {
+        const int64_t f = args.followup;
+        for (int64_t r = 0; r < args.requests; ++r) cu_follow[static_cast<size_t>(r) + 1] = static_cast<int32_t>((r + 1) * f);
+        for (int64_t l = 0; l < args.layers; ++l) {
+            const uint32_t seed = static_cast<uint32_t>(l * 29);
+            fq.push_back(Filled({args.requests * f, kHeadsQ, kHeadDim}, *device, 8000 + seed, 1.0f));
+            fk.push_back(Filled({args.requests * f, kHeadsKv, kHeadDim}, *device, 8100 + seed, 1.0f));
+            fv.push_back(Filled({args.requests * f, kHeadsKv, kHeadDim}, *device, 8200 + seed, 0.5f));
+        }
+        device->synchronize();
+        const auto f0 = std::chrono::steady_clock::now();
+        sca::AttentionConfig follow_cfg;
+        follow_cfg.causal = true;
+        for (int64_t l = 0; l < args.layers; ++l) {
+            sca::PagedKVCache& cache = caches[static_cast<size_t>(l)];
+            for (int64_t r = 0; r < args.requests; ++r) {
+                const int64_t row = kHeadsKv * kHeadDim;
+                sci::Tensor kr(sci::TensorShape({f, kHeadsKv, kHeadDim}), sci::DType::kFloat16, *device,
+                               static_cast<uint16_t*>(fk[static_cast<size_t>(l)].data()) + r * f * row, false);
+                sci::Tensor vr(sci::TensorShape({f, kHeadsKv, kHeadDim}), sci::DType::kFloat16, *device,
+                               static_cast<uint16_t*>(fv[static_cast<size_t>(l)].data()) + r * f * row, false);
+                const sci::Status stored = cache.AppendTokens(r, 0, kr, vr, nullptr);
+                if (!stored.ok()) {
+                    std::printf("[rollout] follow-up append failed: %s\n", stored.ToString().c_str());
+                    return 4;
+                }
+            }
+            if (const sci::Status synced = cache.SyncPageTable(nullptr); !synced.ok()) return 4;
+            auto served = sca::paged_prefill(fq[static_cast<size_t>(l)], cache, args.requests, cu_follow.data(), 0, follow_cfg);
+            if (!served.ok()) {
+                std::printf("[rollout] chunked prefill over the paged cache failed: %s\n", served.error().ToString().c_str());
+                return 4;
+            }
+            if (l == 0) followup_out = std::move(served->out);
+        }
+        device->synchronize();
+        followup_ms = Ms(f0, std::chrono::steady_clock::now());
+    }
+
     const double prefill_ms = Ms(t0, t1), decode_ms = Ms(t1b, t2);
     sci::Tensor& last_q = q_steps[0];
     const int64_t generated = args.requests * args.new_tokens;
@@ -243,6 +348,18 @@ int main(int argc, char** argv) {
     std::printf("[rollout] decode : %lld steps x %lld layers in %.2f ms -> %.0f generated tokens/s (%.3f ms per step)\n",
                 static_cast<long long>(args.new_tokens), static_cast<long long>(args.layers), decode_ms,
                 1000.0 * static_cast<double>(generated) / decode_ms, decode_ms / static_cast<double>(args.new_tokens));
+    const double followup_rate =
+        followup_ms > 0.0 ? 1000.0 * static_cast<double>(args.requests * args.followup * args.layers) / followup_ms : 0.0;
+    if (args.followup > 0) {
+        std::printf("[rollout] follow-up: %lld requests x %lld new tokens x %lld layers over the paged cache in %.2f ms -> %.0f tokens/s per layer\n",
+                    static_cast<long long>(args.requests), static_cast<long long>(args.followup),
+                    static_cast<long long>(args.layers), followup_ms, followup_rate);
+    }
+    if (args.shard >= 0) {
+        std::printf("[rollout-rates] prefill=%.1f decode=%.1f followup=%.1f\n",
+                    1000.0 * static_cast<double>(prompt_tokens * args.layers) / prefill_ms,
+                    1000.0 * static_cast<double>(generated) / decode_ms, followup_rate);
+    }
     const sca::KVCacheStats stats = caches[0].Stats();
     std::printf("[rollout] layer 0 cache: %lld of %lld blocks used, %lld appends\n", static_cast<long long>(stats.used_blocks),
                 static_cast<long long>(stats.num_blocks), static_cast<long long>(stats.num_appends));
@@ -258,8 +375,8 @@ int main(int argc, char** argv) {
         dense_cfg.layout = sca::AttnLayout::kBSHD;
         double worst = 0.0;
         for (int64_t r = 0; r < args.requests; ++r) {
-            const int64_t len = cache.SeqLength(r);
-            const int64_t nblk = cache.LogicalBlockCount(r);
+            const int64_t len = decode_len[static_cast<size_t>(r)];
+            const int64_t nblk = (len + kBlockSize - 1) / kBlockSize;
             const int32_t* ids = cache.PageTableDevicePtr() + r * cache.MaxBlocksPerSeq();
             auto gk = cache.Storage().GatherK(0, ids, nblk, nullptr);
             auto gv = cache.Storage().GatherV(0, ids, nblk, nullptr);
@@ -284,6 +401,49 @@ int main(int argc, char** argv) {
         std::printf("[rollout] verify: paged vs contiguous decode, max abs difference %.3e over %lld requests\n", worst,
                     static_cast<long long>(args.requests));
         if (!(worst <= 2e-3)) return 5;
+        if (args.followup > 0) {
+            // follow-up outputs of the first requests vs. the flash backend on the gathered cache (S_q < S_kv, causal)
+            const int64_t f = args.followup, checked = std::min<int64_t>(args.requests, 4);
+            sca::AttentionConfig flash_cfg;
+            flash_cfg.backend = sca::BackendKind::kFlash;
+            flash_cfg.causal = true;
+            flash_cfg.layout = sca::AttnLayout::kBSHD;
+            std::vector<uint16_t> got(static_cast<size_t>(checked * f * kHeadsQ * kHeadDim));
+            device->copy_to_host(got.data(), followup_out.data(), got.size() * sizeof(uint16_t));
+            double worst_follow = 0.0;
+            for (int64_t r = 0; r < checked; ++r) {
+                const int64_t len = cache.SeqLength(r);
+                const int64_t nblk = cache.LogicalBlockCount(r);
+                const int32_t* ids = cache.PageTableDevicePtr() + r * cache.MaxBlocksPerSeq();
+                auto gk = cache.Storage().GatherK(0, ids, nblk, nullptr);
+                auto gv = cache.Storage().GatherV(0, ids, nblk, nullptr);
+                if (!gk.ok() || !gv.ok()) return 4;
+                sci::Tensor kc = View(*gk, {1, len, kHeadsKv, kHeadDim});
+                sci::Tensor vc = View(*gv, {1, len, kHeadsKv, kHeadDim});
+                sci::Tensor qc(sci::TensorShape({1, f, kHeadsQ, kHeadDim}), sci::DType::kFloat16, *device,
+                               static_cast<uint16_t*>(fq[0].data()) + r * f * kHeadsQ * kHeadDim, false);
+                const auto dense = sca::flash_attention(qc, kc, vc, flash_cfg);
+                if (!dense.ok()) {
+                    std::printf("[rollout] verification prefill failed: %s\n", dense.error().ToString().c_str());
+                    return 4;
+                }
+                // flash returns BHSD [1, H, f, D]; the follow-up output is token-major [f, H, D]
+                std::vector<uint16_t> ref(static_cast<size_t>(f * kHeadsQ * kHeadDim));
+                device->copy_to_host(ref.data(), dense->out.data(), ref.size() * sizeof(uint16_t));
+                for (int64_t t = 0; t < f; ++t) {
+                    for (int64_t h = 0; h < kHeadsQ; ++h) {
+                        for (int64_t e = 0; e < kHeadDim; ++e) {
+                            const float a = FromHalf(ref[static_cast<size_t>((h * f + t) * kHeadDim + e)]);
+                            const float b = FromHalf(got[static_cast<size_t>(((r * f + t) * kHeadsQ + h) * kHeadDim + e)]);
+                            worst_follow = std::max(worst_follow, std::fabs(static_cast<double>(a) - static_cast<double>(b)));
+                        }
+                    }
+                }
+            }
+            std::printf("[rollout] verify: chunked prefill over the paged cache vs flash on the gathered cache, max abs difference %.3e over %lld requests\n",
+                        worst_follow, static_cast<long long>(checked));
+            if (!(worst_follow <= 2e-3)) return 5;
+        }
     }
     return 0;
 }

@@ -585,5 +585,14 @@ SCI_ATTENTION_API sci::Result<AttentionResult> paged_attention(const sci::Tensor
                                                                const AttentionConfig& cfg);
 SCI_ATTENTION_API sci::Result<AttentionResult> paged_attention(const sci::Tensor& q, const PagedKVCache& kv,
                                                                const AttentionConfig& cfg);
+// Addition (no counterpart in the reference, which names it as the step after the packed prefill:
+// docs/flash_attention.md:95): chunked prefill over the paged cache in one launch. `q` holds the NEW tokens of
+// `num_seqs` sequences packed as [total_q, H_q, D] (sequence s = cache slot s); cu_seqlens_q is a HOST int32 array of
+// num_seqs + 1 offsets. The keys and values of those tokens must already be in the cache (AppendTokens, then
+// SyncPageTable): sequence s attends over its kv.SeqLength(s) cached tokens with the bottom-right aligned causal
+// mask. Returns out [total_q, H_q, D]. fp16 / bf16, block sizes 8 / 16 / 32 / 64.
+SCI_ATTENTION_API sci::Result<AttentionResult> paged_prefill(const sci::Tensor& q, const PagedKVCache& kv, int64_t num_seqs,
+                                                             const int32_t* cu_seqlens_q, int64_t layer,
+                                                             const AttentionConfig& cfg);
 
 }  // namespace sca

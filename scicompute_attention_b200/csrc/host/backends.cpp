@@ -5,6 +5,7 @@
 // (src/backends/{naive,tiled,flash,decode,paged}/*_backend.cpp), with the tile / split tables of
 // tables:: (api.cpp) in place of the laptop-GPU ones.
 #include <string>
+#include <vector>
 
 #include "device/cuda_device.hpp"
 #include "internal.hpp"
@@ -799,6 +800,95 @@ sci::Result<AttentionResult> paged_attention(const sci::Tensor& q, const PagedKV
                                              const AttentionConfig& cfg) {
     return RunPaged(q, kv, params, cfg);
 }
+sci::Result<AttentionResult> paged_prefill(const sci::Tensor& q, const PagedKVCache& kv, int64_t num_seqs,
+                                           const int32_t* cu_seqlens_q, int64_t layer, const AttentionConfig& cfg) {
+    const sci::StreamOrderedScope allocations_on_call_stream(StreamHandle(cfg.stream));
+    const KVCacheConfig& kcfg = kv.Storage().Config();
+    if (q.ndims() != 3 || cu_seqlens_q == nullptr) {
+        return Refuse(AttnStatusCode::kShapeMismatch, "paged_prefill expects q=[total_q, H_q, D] and host cu_seqlens_q");
+    }
+    const int64_t total_q = q.dim(0), heads = q.dim(1), d = q.dim(2);
+    if (num_seqs < 1 || num_seqs > kv.MaxNumSeqs()) {
+        return Refuse(AttnStatusCode::kShapeMismatch, "paged_prefill num_seqs=" + std::to_string(num_seqs) +
+                                                          " out of range [1," + std::to_string(kv.MaxNumSeqs()) + "]");
+    }
+    if (layer < 0 || layer >= kcfg.num_layers) {
+        return Refuse(AttnStatusCode::kShapeMismatch, "paged_prefill layer=" + std::to_string(layer) + " out of range [0," +
+                                                          std::to_string(kcfg.num_layers) + ")");
+    }
+    if (q.dtype() != kcfg.dtype || (q.dtype() != sci::DType::kFloat16 && q.dtype() != sci::DType::kBFloat16)) {
+        return Refuse(AttnStatusCode::kUnsupportedDtype, "paged_prefill computes in fp16/bf16 and q must have the cache's dtype");
+    }
+    if (d != kcfg.head_dim || SupportedHeadDimIndex(d) < 0 || kcfg.num_kv_heads < 1 || heads % kcfg.num_kv_heads != 0) {
+        return Refuse(AttnStatusCode::kShapeMismatch, "paged_prefill: q [*, " + std::to_string(heads) + ", " + std::to_string(d) +
+                                                          "] does not fit the cache's heads / head_dim");
+    }
+    if (cu_seqlens_q[0] != 0 || cu_seqlens_q[num_seqs] != total_q) {
+        return Refuse(AttnStatusCode::kShapeMismatch, "paged_prefill: cu_seqlens_q must run from 0 to total_q");
+    }
+    std::vector<int32_t> have(static_cast<size_t>(num_seqs));
+    for (int64_t s = 0; s < num_seqs; ++s) {
+        const int64_t fresh = static_cast<int64_t>(cu_seqlens_q[s + 1]) - cu_seqlens_q[s];
+        have[static_cast<size_t>(s)] = static_cast<int32_t>(kv.SeqLength(s));
+        if (fresh < 1 || kv.SeqLength(s) < fresh) {
+            return Refuse(AttnStatusCode::kShapeMismatch,
+                          "paged_prefill: sequence " + std::to_string(s) + " brings " + std::to_string(fresh) +
+                              " new tokens but the cache holds " + std::to_string(kv.SeqLength(s)) +
+                              " (append the new tokens' K/V first)");
+        }
+    }
+    if (kv.PageTableDevicePtr() == nullptr) {
+        return Refuse(AttnStatusCode::kShapeMismatch, "paged_prefill has no page table (call PagedKVCache::SyncPageTable first)");
+    }
+    AttentionResult result;
+    result.out = sci::Tensor(sci::TensorShape({total_q, heads, d}), q.dtype(), q.device());
+    const long long ws_bytes = sca_flash_varlen_workspace_bytes(num_seqs, total_q);
+    sci::Tensor workspace(sci::TensorShape({static_cast<sci::index_t>(ws_bytes > 0 ? ws_bytes : 16)}), sci::DType::kUInt8, q.device());
+    if (result.out.data() == nullptr || workspace.data() == nullptr) {
+        return Refuse(AttnStatusCode::kWorkspaceExceeded, "allocation of the paged prefill output failed");
+    }
+    AttentionShape shape;
+    shape.batch = num_seqs;
+    shape.seq_q = total_q;
+    shape.seq_kv = total_q;
+    shape.num_heads = heads;
+    shape.num_kv_heads = kcfg.num_kv_heads;
+    shape.head_dim = d;
+    ScaFlashPagedParams p{};
+    p.q = q.data();
+    p.out = result.out.data();
+    p.k_pool = kv.Storage().K(layer).data();
+    p.v_pool = kv.Storage().V(layer).data();
+    p.page_table = kv.PageTableDevicePtr();
+    p.total_q = total_q;
+    p.num_heads = heads;
+    p.num_kv_heads = kcfg.num_kv_heads;
+    p.head_dim = d;
+    p.num_seqs = num_seqs;
+    p.num_blocks = kcfg.num_blocks;
+    p.block_size = kv.BlockSize();
+    p.max_blocks_per_seq = kv.MaxBlocksPerSeq();
+    p.cu_seqlens_q = cu_seqlens_q;
+    p.seq_lens_kv = have.data();
+    p.scale = EffectiveScale(cfg, shape);
+    p.causal = cfg.causal ? 1 : 0;
+    p.dtype_id = DtypeId(q.dtype());
+    p.workspace = workspace.data();
+    p.workspace_bytes = ws_bytes;
+    if (sci::Status s = FromAbi(sca_launch_flash_paged(&p, StreamHandle(cfg.stream))); !s.ok()) {
+        return sci::MakeUnexpected<AttentionResult>(s);
+    }
+    // `workspace` is released when this scope ends: the free is ordered on the call's stream, behind the kernel
+    result.stats.used_backend = BackendKind::kFlash;
+    result.stats.workspace_bytes = 0;
+    result.stats.materialized_score_bytes = 0;
+    result.stats.kv_bytes = kv.Storage().MemoryBytes();
+    result.stats.note = "chunked prefill over the paged cache: " + std::to_string(num_seqs) + " sequences, " +
+                        std::to_string(total_q) + " new tokens, block_size=" + std::to_string(kv.BlockSize()) +
+                        ", layer=" + std::to_string(layer);
+    return sci::Ok(std::move(result));
+}
+
 sci::Result<AttentionResult> paged_attention(const sci::Tensor& q, const PagedKVCache& kv, const AttentionConfig& cfg) {
     PagedAttentionParams params;
     params.page_table = kv.PageTableDevicePtr();

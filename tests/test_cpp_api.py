@@ -59,3 +59,20 @@ def test_rollout_example_serves_and_its_two_decode_backends_agree():
                            "--prompt-max", "300", "--verify"], capture_output=True, text=True, timeout=600)
     assert proc.returncode == 0, proc.stdout[-3000:] + proc.stderr[-2000:]
     assert "verify: paged vs contiguous decode" in proc.stdout and "generated tokens/s" in proc.stdout
+    # follow-up prompts: one chunked-prefill launch per layer over the paged cache, checked against flash on the gathered cache
+    assert "verify: chunked prefill over the paged cache vs flash" in proc.stdout and "follow-up:" in proc.stdout
+
+
+@pytest.mark.gpu
+def test_rollout_example_on_every_visible_gpu():
+    """--gpus G: one copy per GPU on its own requests and caches (no collective); the parent adds up the rates."""
+    import torch
+    gpus = torch.cuda.device_count()
+    if gpus < 2:
+        pytest.skip("needs at least 2 GPUs")
+    proc = subprocess.run([ROLLOUT, "--gpus", str(gpus), "--requests", "8", "--layers", "2", "--new-tokens", "4",
+                           "--prompt-min", "33", "--prompt-max", "200", "--followup", "40", "--verify"],
+                          capture_output=True, text=True, timeout=900)
+    assert proc.returncode == 0, proc.stdout[-3000:] + proc.stderr[-2000:]
+    assert f"{gpus} GPUs together" in proc.stdout
+    assert proc.stdout.count("verify: paged vs contiguous decode") == gpus
