@@ -43,7 +43,8 @@ enum {
     SCA_NOT_IMPLEMENTED = 5,
     SCA_CUDA_ERROR = 100,
     SCA_CUDA_NOT_AVAILABLE = 101,
-    SCA_CUDA_OOM = 102
+    SCA_CUDA_OOM = 102,
+    SCA_TIMEOUT = 500 /* a bounded wait for other ranks ran out (sci::StatusCode::kDeviceError) */
 };
 
 /* Message of the most recent failing call on this thread ("" when none). */
@@ -250,7 +251,7 @@ SCA_ABI int sca_launch_flash_paged(const ScaFlashPagedParams* params, void* stre
  * ordered (one stream). With epoch = 0 the kernel counts the calls itself in the buffer (every rank must then
  * use 0 on every call): the parameters no longer change from step to step, so the step can be captured in a
  * CUDA graph and replayed. peer_buffers[rank] is the rank's own buffer. If a peer does not show up within
- * about a second the kernel gives up, leaves `out` undefined and sets the status word that
+ * about a second the kernel gives up, fills `out` with NaN and records the step in the status word that
  * sca_peer_exchange_status reads back (0 = all waits were satisfied). One process per GPU: ranks that
  * share a GPU would wait on kernels that cannot run at the same time. */
 #define SCA_PEER_MAX_RANKS 16
@@ -274,8 +275,30 @@ SCA_ABI int sca_peer_buffer_create(int64_t bytes, void** device_ptr, unsigned ch
 SCA_ABI int sca_peer_buffer_open(const unsigned char* handle_in, void** device_ptr);
 SCA_ABI int sca_peer_buffer_close(void* device_ptr);   /* a buffer mapped with _open */
 SCA_ABI int sca_peer_buffer_destroy(void* device_ptr); /* a buffer made with _create */
+/* 0 = every wait so far was satisfied; otherwise the epoch (step number, from 1) of the first launch that gave up
+ * waiting for a peer - that launch wrote NaN instead of a result. The value stays until sca_peer_exchange_clear.
+ * Both calls synchronise with the device. */
 SCA_ABI int sca_peer_exchange_status(const void* local_buffer, int32_t* status_out);
+SCA_ABI int sca_peer_exchange_clear(void* local_buffer);
 SCA_ABI int sca_launch_seqsplit_exchange(const ScaSeqSplitExchange* params, void* stream);
+
+/* Multi-GPU plumbing with bounded waits (no counterpart in the reference, which is single-GPU): a NCCL communicator
+ * for the all-gather of the (m, l, O) triples between sca_launch_decode_triples and sca_launch_merge_triples.
+ * NCCL is loaded at run time (libnccl.so.2, or the file the environment variable SCA_NCCL_LIBRARY names); without it
+ * the calls return SCA_NOT_IMPLEMENTED. One process per GPU; rank 0 makes the id (sca_mgpu_unique_id) and hands its
+ * 128 bytes to the other ranks over any host channel. The communicator is non-blocking: sca_mgpu_init waits at most
+ * `timeout_ms` for the other ranks, sca_mgpu_allgather_triples at most `timeout_ms` for the collective to complete
+ * (timeout_ms <= 0: it only enqueues and returns; the caller orders later work on `stream`). When a limit passes,
+ * the communicator is aborted - which also releases a collective kernel that is waiting for a peer - and the call
+ * returns SCA_TIMEOUT; an aborted communicator only accepts sca_mgpu_destroy.
+ *   gathered [world][floats_per_rank] <- mine [floats_per_rank] of every rank, rank-major (fp32, device memory). */
+#define SCA_MGPU_ID_BYTES 128
+SCA_ABI int sca_mgpu_unique_id(unsigned char* id_out);
+SCA_ABI int sca_mgpu_init(const unsigned char* id, int32_t rank, int32_t world, int32_t timeout_ms, void** comm_out);
+SCA_ABI int sca_mgpu_allgather_triples(void* comm, const float* mine, float* gathered, int64_t floats_per_rank,
+                                       void* stream, int32_t timeout_ms);
+SCA_ABI int sca_mgpu_abort(void* comm);
+SCA_ABI int sca_mgpu_destroy(void* comm);
 
 /* Allocation-free split-K decode. No counterpart in the reference.
  *

@@ -13,7 +13,8 @@ KERNEL_LIB = os.path.join(PKG, "libsca_b200.so")
 DTYPE_F32, DTYPE_F16, DTYPE_BF16 = 0, 1, 2
 SCA_OK = 0
 STATUS_NAMES = {0: "OK", 4: "InvalidArgument", 5: "NotImplemented", 100: "CudaError",
-                101: "CudaNotAvailable", 102: "CudaOutOfMemory"}
+                101: "CudaNotAvailable", 102: "CudaOutOfMemory", 500: "Timeout"}
+MGPU_ID_BYTES = 128
 
 # every symbol include/sca_b200.h declares (tests check that the library exports all of them)
 EXPORTED_SYMBOLS = [
@@ -23,8 +24,9 @@ EXPORTED_SYMBOLS = [
     "sca_launch_simt_forward", "sca_naive_score_bytes", "sca_launch_naive_forward", "sca_launch_kv_append", "sca_launch_kv_reset_block",
     "sca_launch_kv_gather", "sca_launch_kv_append_batched", "sca_launch_decode_partials",
     "sca_peer_buffer_bytes", "sca_peer_buffer_create", "sca_peer_buffer_open", "sca_peer_buffer_close",
-    "sca_peer_buffer_destroy", "sca_peer_exchange_status", "sca_launch_seqsplit_exchange",
+    "sca_peer_buffer_destroy", "sca_peer_exchange_status", "sca_peer_exchange_clear", "sca_launch_seqsplit_exchange",
     "sca_flash_varlen_workspace_bytes", "sca_launch_flash_varlen", "sca_launch_flash_paged",
+    "sca_mgpu_unique_id", "sca_mgpu_init", "sca_mgpu_allgather_triples", "sca_mgpu_abort", "sca_mgpu_destroy",
 ]
 
 PEER_MAX_RANKS = 16
@@ -159,6 +161,11 @@ def lib() -> C.CDLL:
     l.sca_flash_varlen_workspace_bytes.restype = C.c_longlong
     l.sca_launch_flash_varlen.argtypes = [C.POINTER(FlashVarlenParams), C.c_void_p]
     l.sca_launch_flash_paged.argtypes = [C.POINTER(FlashPagedParams), C.c_void_p]
+    l.sca_mgpu_unique_id.argtypes = [C.c_char_p]
+    l.sca_mgpu_init.argtypes = [C.c_char_p, C.c_int32, C.c_int32, C.c_int32, C.POINTER(C.c_void_p)]
+    l.sca_mgpu_allgather_triples.argtypes = [C.c_void_p, C.c_void_p, C.c_void_p, C.c_int64, C.c_void_p, C.c_int32]
+    l.sca_mgpu_abort.argtypes = [C.c_void_p]
+    l.sca_mgpu_destroy.argtypes = [C.c_void_p]
     l.sca_launch_decode_partials.argtypes = [C.POINTER(DecodeFwdParams), C.c_void_p]
     l.sca_peer_buffer_bytes.argtypes = [C.c_int32, C.c_int64, C.c_int64]
     l.sca_peer_buffer_bytes.restype = C.c_longlong

@@ -76,7 +76,7 @@ def build_kernels(force: bool = False, verbose: bool = False) -> str:
         with cf.ThreadPoolExecutor(max_workers=min(8, len(jobs))) as pool:
             list(pool.map(_run, jobs))
     if jobs or not os.path.exists(KERNEL_LIB):
-        _run([nvcc, "-shared", "-o", KERNEL_LIB] + objs + ["-cudart", "static"])
+        _run([nvcc, "-shared", "-o", KERNEL_LIB] + objs + ["-cudart", "static", "-ldl"])
     if verbose:
         print("built", KERNEL_LIB)
     return KERNEL_LIB

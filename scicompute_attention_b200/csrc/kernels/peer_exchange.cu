@@ -136,7 +136,8 @@ seqsplit_exchange_kernel(const ExchangeParams p) {
             while (static_cast<int>(LoadAcquireSys(flags + s) - epoch) < 0) {
                 if (clock64() - start > kPeerWaitCycles) {
                     ok = 0;
-                    *reinterpret_cast<int*>(local + kStatusOffset) = 1;
+                    // remember the first step that gave up (the epoch; never 0) until the host clears it
+                    atomicCAS(reinterpret_cast<int*>(local + kStatusOffset), 0, static_cast<int>(epoch));
                     break;
                 }
                 __nanosleep(64);
@@ -145,7 +146,18 @@ seqsplit_exchange_kernel(const ExchangeParams p) {
         s_ok = ok;
     }
     __syncthreads();
-    if (!s_ok) return;  // the output of this launch is invalid; the host reads the status word
+    if (!s_ok) {
+        // a peer did not show up: this launch has no result. The rows this CTA owns are filled with NaN so that stale
+        // values of an earlier step cannot pass as an answer; the host learns the step from the status word.
+        for (int row = blockIdx.x; row < p.rows; row += gridDim.x) {
+#pragma unroll
+            for (int c = 0; c < kCols; ++c) {
+                const int d = threadIdx.x + 128 * c;
+                if (d < p.head_dim) reinterpret_cast<T*>(p.out)[static_cast<size_t>(row) * p.head_dim + d] = FromFloat<T>(CUDART_NAN_F);
+            }
+        }
+        return;
+    }
 
     // 4. merge over ranks
     const float* data = reinterpret_cast<const float*>(local + kHeaderBytes) + slot;
@@ -245,6 +257,15 @@ extern "C" int sca_peer_exchange_status(const void* local_buffer, int32_t* statu
         return FailCuda(e, "cudaMemcpy(peer status)");
     }
     *status_out = value;
+    return SCA_OK;
+}
+
+extern "C" int sca_peer_exchange_clear(void* local_buffer) {
+    ClearError();
+    if (local_buffer == nullptr) return Fail(SCA_INVALID_ARGUMENT, "peer status: null pointer");
+    if (cudaError_t e = cudaMemset(static_cast<unsigned char*>(local_buffer) + kStatusOffset, 0, sizeof(int)); e != cudaSuccess) {
+        return FailCuda(e, "cudaMemset(peer status)");
+    }
     return SCA_OK;
 }
 

@@ -42,13 +42,63 @@ def kv_range_for_rank(seq_kv: int, rank: int, world: int) -> tuple[int, int]:
     return lo, lo + base + (1 if rank < extra else 0)
 
 
+class MgpuComm:
+    """The library's own NCCL communicator (sca_mgpu_*): non-blocking, every wait for other ranks bounded by
+    `timeout_ms`, after which the communicator is aborted and the call raises ScaError(code 500) instead of hanging.
+
+    Collective constructor: rank 0 makes the 128-byte id and `share_id(id_or_None) -> id` hands it to everybody (by
+    default through torch.distributed's object broadcast, i.e. over the host side of the process group)."""
+
+    def __init__(self, rank: int, world: int, *, timeout_ms: int = 10000, share_id: Callable | None = None):
+        import ctypes as C
+        from . import _lib
+        self._lib, self._C = _lib, C
+        self.rank, self.world, self.timeout_ms = rank, world, timeout_ms
+        l = _lib.lib()
+        ident = None
+        if rank == 0:
+            buf = C.create_string_buffer(_lib.MGPU_ID_BYTES)
+            _lib.check(l.sca_mgpu_unique_id(buf))
+            ident = bytes(buf.raw)
+        if share_id is None:
+            import torch.distributed as dist
+            box = [ident]
+            dist.broadcast_object_list(box, src=0)
+            ident = box[0]
+        else:
+            ident = share_id(ident)
+        handle = C.c_void_p()
+        _lib.check(l.sca_mgpu_init(ident, rank, world, timeout_ms, C.byref(handle)))
+        self._comm = handle
+
+    def allgather_triples(self, mine, *, stream=None, timeout_ms: int | None = None):
+        """mine fp32 [rows, width] on the device -> [world, rows, width], rank-major. timeout_ms <= 0: enqueue only."""
+        import torch
+        from . import ops
+        rows, width = mine.shape
+        out = torch.empty((self.world, rows, width), dtype=torch.float32, device=mine.device)
+        limit = self.timeout_ms if timeout_ms is None else timeout_ms
+        self._lib.check(self._lib.lib().sca_mgpu_allgather_triples(self._comm, mine.contiguous().data_ptr(), out.data_ptr(),
+                                                                   rows * width, ops._stream_ptr(stream), limit))
+        return out
+
+    def abort(self):
+        self._lib.check(self._lib.lib().sca_mgpu_abort(self._comm))
+
+    def close(self):
+        if self._comm is not None:
+            self._lib.check(self._lib.lib().sca_mgpu_destroy(self._comm))
+            self._comm = None
+
+
 def sequence_split_decode(q, k_shard, v_shard, *, group=None, scale=None, num_splits: int = 0,
                           triples_fn: Callable | None = None, merge_fn: Callable | None = None,
-                          empty_triples_fn: Callable | None = None):
+                          empty_triples_fn: Callable | None = None, comm: "MgpuComm | None" = None):
     """Decode attention with the KV sequence sharded over the ranks of `group`.
 
     q [B, H_q, 1, D] is replicated; k_shard / v_shard [B, H_kv, S_local, D] hold this rank's token range
-    (S_local may be 0). Returns the normalised output [B * H_q, D] on every rank.
+    (S_local may be 0). Returns the normalised output [B * H_q, D] on every rank. The triples travel through `comm`
+    (the library's bounded NCCL communicator, MgpuComm) when one is given, else through torch.distributed.
     `triples_fn`, `merge_fn` and `empty_triples_fn` default to the CUDA operators; the CPU tests of the
     plumbing inject host implementations.
     """
@@ -69,7 +119,10 @@ def sequence_split_decode(q, k_shard, v_shard, *, group=None, scale=None, num_sp
         mine = torch.zeros((b * hq, 2 + d), dtype=torch.float32, device=q.device)
         mine[:, 0] = float("-inf")
     world = dist.get_world_size(group) if dist.is_available() and dist.is_initialized() else 1
-    if world == 1:
+    if comm is not None:
+        # the library's own communicator: enqueue only (the merge kernel follows on the same stream)
+        gathered = comm.allgather_triples(mine, timeout_ms=0) if comm.world > 1 else mine.unsqueeze(0)
+    elif world == 1:
         gathered = mine.unsqueeze(0)
     else:
         rows, width = mine.shape
@@ -177,11 +230,20 @@ class PeerExchange:
         return graph, out
 
     def status(self) -> int:
-        """0, or 1 if some launch gave up waiting for a peer (synchronises the device)."""
+        """0, or the step (from 1) of the first launch that gave up waiting for a peer; that launch wrote NaN instead
+        of a result. Synchronises the device. Call it at the cadence results are consumed - after every step when
+        each output is used at once, after a batch of graph replays otherwise."""
         import ctypes as C
         value = C.c_int32(0)
         self._lib.check(self._lib.lib().sca_peer_exchange_status(self._own, C.byref(value)))
         return int(value.value)
+
+    def check(self) -> None:
+        """Raises when a step since the last check gave up waiting for a peer, and clears the record."""
+        step = self.status()
+        if step != 0:
+            self._lib.check(self._lib.lib().sca_peer_exchange_clear(self._own))
+            raise self._lib.ScaError(500, f"sequence-split exchange: step {step} gave up waiting for a peer; its output is NaN")
 
     def close(self):
         """Collective: unmaps the peers' buffers, then frees the own one."""

@@ -44,6 +44,17 @@ def _worker(rank, world, port, result_dir):
     expect = ol.attention_f64(qd, kd, vd, causal=True)
     H.check_close(H.to_host_f32(out).reshape(b, hq, 1, d), expect, dt, f"sequence-split decode rank {rank}")
 
+    # the same through the library's own bounded NCCL communicator (C ABI sca_mgpu_*): identical bits, because the
+    # same triples are merged by the same kernel
+    comm = mg.MgpuComm(rank, world, timeout_ms=20000)
+    out_c = mg.sequence_split_decode(q, k, v, comm=comm)
+    torch.cuda.synchronize()
+    assert torch.equal(out_c.view(torch.int16), out.view(torch.int16))
+    mine = torch.full((4, 6), float(rank), dtype=torch.float32, device=f"cuda:{rank}")
+    both = comm.allgather_triples(mine)          # bounded completion wait inside the call
+    assert [float(both[r].mean()) for r in range(world)] == [float(r) for r in range(world)]
+    comm.close()
+
     # the same through the peer-memory kernel, three steps with different keys (both buffer halves get reused)
     px = mg.PeerExchange(b * hq, d, f"cuda:{rank}")
     for step in range(3):
@@ -78,6 +89,31 @@ def _worker(rank, world, port, result_dir):
         f.write("ok")
     dist.barrier()
     dist.destroy_process_group()
+
+
+def test_a_rank_that_never_joins_gives_a_timeout_status_not_a_hang():
+    """Real NCCL, one process, one GPU: rank 0 of a 2-rank communicator whose rank 1 does not exist. The wait is on
+    the host (communicator set-up never completes); after the limit the library aborts and returns SCA_TIMEOUT."""
+    import ctypes as C
+    import time
+
+    import torch
+    from scicompute_attention_b200 import _lib
+    if not torch.cuda.is_available():
+        pytest.skip("needs a GPU")
+    torch.cuda.set_device(0)
+    torch.zeros(1, device="cuda")
+    l = _lib.lib()
+    ident = C.create_string_buffer(_lib.MGPU_ID_BYTES)
+    _lib.check(l.sca_mgpu_unique_id(ident))
+    comm = C.c_void_p()
+    t0 = time.time()
+    rc = l.sca_mgpu_init(ident.raw, 0, 2, 1500, C.byref(comm))
+    took = time.time() - t0
+    assert rc == 500 and comm.value is None, (rc, l.sca_last_error())
+    assert 1.4 <= took < 30.0 and b"aborted" in l.sca_last_error()
+    # the device is still fine
+    assert float(torch.ones(8, device="cuda").sum()) == 8.0
 
 
 def test_sequence_split_decode_over_nccl_and_over_peer_memory(tmp_path):

@@ -97,7 +97,10 @@ def test_single_rank_exchange_equals_split_k_decode_and_a_missing_peer_times_out
     out = torch.empty((rows, d), dtype=q.dtype, device=q.device)
     _lib.check(_exchange([mine, ghost], 0, 2, rows, d, splits, 1, pm, pl, po, out))
     torch.cuda.synchronize()
-    assert _status(mine) == 1
+    assert _status(mine) == 1                      # the step (epoch) that gave up
+    assert torch.isnan(out.float()).all()          # no stale values pass as a result
+    _lib.check(_lib.lib().sca_peer_exchange_clear(mine))
+    assert _status(mine) == 0
     # the context is intact: the ordinary operator still works afterwards
     again = ops.decode_attention(q, k, v)
     torch.cuda.synchronize()
