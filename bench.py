@@ -490,6 +490,7 @@ class LongContextWorkload(Workload):
             self.graphs = [self.px.capture(self.q, k, v) for k, v in self.sets]
         elif world > 1:
             self.launches_per_step = 3  # partial, merge to triples, merge over ranks (+ the NCCL all-gather)
+            self.comm = multi_gpu.MgpuComm(rank, world)  # the library's own bounded communicator (sca_mgpu_*)
 
     def step(self):
         k, v = self.sets[self.turn]
@@ -497,7 +498,7 @@ class LongContextWorkload(Workload):
             graph, self.out = self.graphs[self.turn]
             graph.replay()
         elif self.world > 1:
-            self.out = self.mg.sequence_split_decode(self.q, k, v)
+            self.out = self.mg.sequence_split_decode(self.q, k, v, comm=self.comm)
         else:
             self.out = self.ops.decode_attention(self.q, k, v)
         self.turn = (self.turn + 1) % len(self.sets)
@@ -513,7 +514,7 @@ class LongContextWorkload(Workload):
                 "head_dim": self.d, "l2_policy": "inputs larger than L2 (%d x %.0f MB per GPU, used in rotation)" % (copies, mine / 1e6),
                 "sharding": "KV sequence split across ranks; (m, l, O) triples exchanged " +
                             ("by peer stores inside the merge kernel (captured graph)" if self.px is not None else
-                             "by one NCCL all-gather per step" if self.world > 1 else "locally (one rank)")}
+                             "by one NCCL all-gather per step (sca_mgpu communicator)" if self.world > 1 else "locally (one rank)")}
 
     def e2e_setup(self, torch):
         self.hq = self.q.cpu().pin_memory()
@@ -539,8 +540,12 @@ class LongContextWorkload(Workload):
     def teardown(self):
         if self.px is not None:
             self.graphs = None
+            self.px.check()  # raises if some step gave up waiting for a peer
             self.px.close()
             self.px = None
+        if getattr(self, "comm", None) is not None:
+            self.comm.close()
+            self.comm = None
 
 
 class KvWorkload(Workload):

@@ -174,6 +174,7 @@ def lib() -> C.CDLL:
     l.sca_peer_buffer_close.argtypes = [C.c_void_p]
     l.sca_peer_buffer_destroy.argtypes = [C.c_void_p]
     l.sca_peer_exchange_status.argtypes = [C.c_void_p, C.POINTER(C.c_int32)]
+    l.sca_peer_exchange_clear.argtypes = [C.c_void_p]
     l.sca_launch_seqsplit_exchange.argtypes = [C.POINTER(SeqSplitExchange), C.c_void_p]
     _lib = l
     return l
