@@ -133,19 +133,23 @@ def build_cpp_tests(force: bool = False, verbose: bool = False) -> str | None:
 
 
 def build_examples(force: bool = False, verbose: bool = False) -> str | None:
-    """examples/rollout_engine.cpp -> examples/rollout_engine (public C++ API only)."""
-    src = os.path.join(ROOT, "examples", "rollout_engine.cpp")
-    if not os.path.exists(src) or not os.path.exists(HOST_LIB):
+    """examples/*.cpp -> examples/<name> (public C++ API only; bench_attention also uses CUDA events)."""
+    if not os.path.exists(HOST_LIB):
         return None
-    exe = os.path.join(ROOT, "examples", "rollout_engine")
-    if force or not _newer(exe, [src, HOST_LIB] + _headers()):
-        cxx = shutil.which("g++") or "g++"
-        _run([cxx, "-O2", "-std=c++20", "-Wall", "-I", INCLUDE, "-I", os.path.join(INCLUDE, "sci_infra"), src, "-o", exe,
-              "-L", PKG, "-l:libsci_attention.so", "-l:libsca_b200.so",
-              "-Wl,-rpath,$ORIGIN/../scicompute_attention_b200"])
-    if verbose:
-        print("built", exe)
-    return exe
+    cxx = shutil.which("g++") or "g++"
+    cuda = os.path.dirname(os.path.dirname(_nvcc()))
+    last = None
+    for src in sorted(glob.glob(os.path.join(ROOT, "examples", "*.cpp"))):
+        exe = os.path.splitext(src)[0]
+        if force or not _newer(exe, [src, HOST_LIB] + _headers()):
+            _run([cxx, "-O2", "-std=c++20", "-Wall", "-I", INCLUDE, "-I", os.path.join(INCLUDE, "sci_infra"),
+                  "-I", os.path.join(cuda, "include"), src, "-o", exe, "-L", PKG, "-l:libsci_attention.so",
+                  "-l:libsca_b200.so", "-L", os.path.join(cuda, "lib64"), "-lcudart_static", "-lrt", "-ldl", "-lpthread",
+                  "-Wl,-rpath,$ORIGIN/../scicompute_attention_b200"])
+        if verbose:
+            print("built", exe)
+        last = exe
+    return last
 
 
 def build_all(force: bool = False, verbose: bool = False) -> None:

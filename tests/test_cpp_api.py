@@ -76,3 +76,33 @@ def test_rollout_example_on_every_visible_gpu():
     assert proc.returncode == 0, proc.stdout[-3000:] + proc.stderr[-2000:]
     assert f"{gpus} GPUs together" in proc.stdout
     assert proc.stdout.count("verify: paged vs contiguous decode") == gpus
+
+
+@pytest.mark.gpu
+def test_api_level_benchmark_writes_the_reference_record_format(tmp_path):
+    """examples/bench_attention times one public API call per sample and writes the JSON / CSV records of the
+    reference's benchmark suite (benchmarks/common/bench_utils.hpp:261-330): same keys, same CSV header."""
+    import json
+    exe = os.path.join(ROOT, "examples", "bench_attention")
+    if not os.path.exists(exe):
+        from scicompute_attention_b200 import build
+        build.build_all()
+    proc = subprocess.run([exe, "--small", "--runs", "10", "--warmup", "3", "--out-dir", str(tmp_path)],
+                          capture_output=True, text=True, timeout=600)
+    assert proc.returncode == 0, proc.stdout[-3000:] + proc.stderr[-2000:]
+    record = json.load(open(tmp_path / "bench_attention.json"))
+    for key in ("benchmark_name", "git_sha", "build_type", "gpu", "compute_cap", "driver", "cuda", "sm_clock_mhz",
+                "timestamp", "warmup", "runs", "seed", "cases"):
+        assert key in record, key
+    assert record["runs"] == 10 and len(record["cases"]) == 4
+    for case in record["cases"]:
+        for key in ("case_id", "impl", "params", "latency_ms", "flops_effective", "tflops", "bytes_moved_modeled",
+                    "effective_bw_gbps", "peak_mem_mb", "workspace_mb", "registers_per_thread", "smem_bytes",
+                    "achieved_occupancy_pct", "reference_max_abs_err", "note"):
+            assert key in case, key
+        lat = case["latency_ms"]
+        assert set(lat) == {"mean", "median", "std", "p50", "p90", "p95", "p99"}
+        assert 0 < lat["p50"] <= lat["p90"] <= lat["p99"]
+    header = open(tmp_path / "bench_attention.csv").readline().strip()
+    assert header == ("name,case_id,warmup,runs,mean_ms,median_ms,std_ms,p50_ms,p90_ms,p95_ms,p99_ms,tflops,"
+                      "effective_bw_gbps,peak_mem_mb,unit")
