@@ -620,7 +620,7 @@ class KvWorkload(Workload):
 def build_workloads(args, world):
     """(primary, [secondary...]) as factories, in run order."""
     single = {
-        "flash": lambda: FlashWorkload(args.dtype),
+        "flash": lambda: FlashWorkload(args.dtype, head_dim=args.head_dim),
         "decode": lambda: DecodeWorkload(),
         "paged": lambda: PagedWorkload(),
         "longctx": lambda: LongContextWorkload(exchange=args.exchange),
@@ -824,9 +824,11 @@ def main():
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
     ap.add_argument("--workload", default="all", choices=["all", "flash", "decode", "paged", "longctx", "kvfill"])
     ap.add_argument("--no-secondary", action="store_true", help="headline only")
+    ap.add_argument("--no-cpu", action="store_true", help="skip the timed host-side legs (for runs under a profiler)")
     ap.add_argument("--e2e-steps", type=int, default=0, help="0 = min(steps, 5)")
     ap.add_argument("--seed", type=int, default=0)
     ap.add_argument("--dtype", default="bf16", choices=["bf16", "fp16"], help="--workload flash only")
+    ap.add_argument("--head-dim", type=int, default=128, choices=[64, 128, 256], help="--workload flash only")
     ap.add_argument("--exchange", default="peer", choices=["peer", "nccl"],
                     help="--workload longctx on more than one GPU: how the triples cross NVLink")
     ap.add_argument("--capture", action="store_true",
@@ -867,7 +869,7 @@ def main():
             primary.NSEQ, primary.NBLK = 32, 20000
         primary.name += "_capture"
         primary.traffic_bytes = None
-    head = measure(primary, args, args.steps, repeats, ctx, with_cpu=True)
+    head = measure(primary, args, args.steps, repeats, ctx, with_cpu=not args.no_cpu)
     del primary
     gc.collect()
     torch.cuda.empty_cache()
@@ -879,7 +881,8 @@ def main():
             wl = make()
             # one CPU leg per workload family (the headline already carries the prefill one)
             family = type(wl).__name__
-            with_cpu = family in ("DecodeWorkload", "PagedWorkload", "LongContextWorkload") and family not in cpu_done
+            with_cpu = (family in ("DecodeWorkload", "PagedWorkload", "LongContextWorkload") and family not in cpu_done
+                        and not args.no_cpu)
             cpu_done.add(family)
             entry = measure(wl, args, wl.default_steps, repeats, ctx, with_cpu=with_cpu)
             if entry is not None:
@@ -914,7 +917,7 @@ def reference_arm(args, rank, world, threads):
     import numpy as np
     import torch
     name = "flash" if args.workload == "all" else args.workload
-    wl = {"flash": lambda: FlashWorkload(args.dtype), "decode": DecodeWorkload, "paged": PagedWorkload,
+    wl = {"flash": lambda: FlashWorkload(args.dtype, head_dim=args.head_dim), "decode": DecodeWorkload, "paged": PagedWorkload,
           "longctx": lambda: LongContextWorkload(exchange=args.exchange), "kvfill": None}[name]
     if wl is None:
         print(json.dumps({"impl": "reference", "unavailable": "the reference has no CPU implementation of the KV kernels"}), flush=True)
