@@ -163,8 +163,9 @@ class FlashWorkload(Workload):
         self.scaling = "strong" if strong else "weak"
         self.name = f"flash_prefill_causal_B{batch}_S{seq}_Hq{HQ}_Hkv{HKV}_D{head_dim}_{dtype_name}" + ("_strong" if strong else "")
         # dram__bytes_read + dram__bytes_write of flash_fwd_sm100_kernel, ncu capture at B=1 scaled x4
-        # (profiles/flash_prefill_c2.md); the output mostly stays in L2 until after the kernel
-        self.traffic_bytes = (50.41e6 + 2.9e6) * batch if (head_dim == 128 and not strong) else None
+        # (profiles/flash_prefill_c2.md, _d64.md, _d256.md); the output mostly stays in L2 until after the kernel
+        captured = {128: 50.43e6 + 3.60e6, 64: 25.22e6 + 0.01e6, 256: 102.76e6 + 27.78e6}  # read + written at B=1
+        self.traffic_bytes = captured[head_dim] * batch if not strong else None
 
     def setup(self, torch, device, seed, rank, world):
         from scicompute_attention_b200 import ops
@@ -271,7 +272,7 @@ class DecodeWorkload(Workload):
         self.name = f"splitk_decode_B{batch}_Skv{seq}_Hq{HQ}_Hkv{HKV}_D{D}_bf16" + ("_strong" if strong else "")
         # dram__bytes_read + dram__bytes_write of decode_partial_kernel, ncu capture at B=16 scaled by the batch
         # (profiles/decode_splitk_c3.md); traffic grows in proportion to the batch
-        self.traffic_bytes = (268.61e6 + 5.8e6) * batch / 16 if not strong else None
+        self.traffic_bytes = (268.71e6 + 3.96e6) * batch / 16 if not strong else None
 
     def setup(self, torch, device, seed, rank, world):
         from scicompute_attention_b200 import ops
@@ -336,9 +337,9 @@ class PagedWorkload(Workload):
     metric, unit, bound = "paged_decode_kv_bandwidth", "GB/s", "hbm"
     launches_per_step = 3  # batched append + partial + merge
     default_steps = 30
-    # ncu capture of the paged decode_partial_kernel on 32 sequences: 606.3 MB moved for 597.7 MB of K/V
+    # ncu capture of the paged decode_partial_kernel on 32 sequences: 602.5 MB moved for 597.7 MB of K/V
     # (profiles/paged_decode_c4.md); scaled by the tokens of the full batch
-    traffic_ratio = (598.10e6 + 8.21e6) / 597.75e6
+    traffic_ratio = (598.31e6 + 4.20e6) / 597.75e6
 
     def __init__(self, strong=False, nseq=256, nblk=160000):
         self.strong, self.NSEQ, self.NBLK, self.BS = strong, nseq, nblk, 16
