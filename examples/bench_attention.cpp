@@ -10,7 +10,7 @@
 //
 // FLOPs are counted for the pairs the mask leaves visible: causal rows see S_kv - S_q + i + 1 keys, i.e.
 // 4 * B * H_q * D * (S_q * (S_kv - S_q) + S_q (S_q + 1) / 2). (The reference's own causal path multiplies the pair
-// count by B * H_q a second time: benchmarks/common/bench_utils.hpp, noted in its survey; not reproduced here.)
+// count by B * H_q a second time, benchmarks/common/bench_utils.hpp; that is not reproduced here.)
 //
 //   bench_attention [--runs N] [--warmup W] [--out-dir DIR] [--small]
 // --small runs reduced shapes (a smoke test of the tool itself). Exit codes: 0 ok, 2 no GPU, 4 a call failed.
