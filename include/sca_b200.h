@@ -287,7 +287,7 @@ SCA_ABI int sca_launch_seqsplit_exchange(const ScaSeqSplitExchange* params, void
  * NCCL is loaded at run time (libnccl.so.2, or the file the environment variable SCA_NCCL_LIBRARY names); without it
  * the calls return SCA_NOT_IMPLEMENTED. One process per GPU; rank 0 makes the id (sca_mgpu_unique_id) and hands its
  * 128 bytes to the other ranks over any host channel. The communicator is non-blocking: sca_mgpu_init waits at most
- * `timeout_ms` for the other ranks, sca_mgpu_allgather_triples at most `timeout_ms` for the collective to complete
+ * `timeout_ms` for the other ranks (<= 0: one minute), sca_mgpu_allgather_triples at most `timeout_ms` for the collective to complete
  * (timeout_ms <= 0: it only enqueues and returns; the caller orders later work on `stream`). When a limit passes,
  * the communicator is aborted - which also releases a collective kernel that is waiting for a peer - and the call
  * returns SCA_TIMEOUT; an aborted communicator only accepts sca_mgpu_destroy.

@@ -136,7 +136,8 @@ extern "C" int sca_mgpu_init(const unsigned char* id, int32_t rank, int32_t worl
         delete c;
         return FailNccl(api, rc, "ncclCommInitRankConfig");
     }
-    if (int wait = WaitForCommunicator(api, c, timeout_ms, "mgpu init")) {
+    // a non-positive limit means the default of one minute: set-up never waits without a bound
+    if (int wait = WaitForCommunicator(api, c, timeout_ms > 0 ? timeout_ms : 60000, "mgpu init")) {
         delete c;  // aborted above when it timed out or failed
         return wait;
     }
