@@ -221,24 +221,35 @@ class FlashWorkload(Workload):
         self.ho = torch.empty(self.q.shape, dtype=self.q.dtype).pin_memory()
         self.h2d = (self.hq.numel() + self.hk.numel() + self.hv.numel()) * 2
         self.d2h = self.ho.numel() * 2
-        self.e2e_streams = [torch.cuda.Stream() for _ in range(self.q.shape[0])]
+        # pieces of the pipeline: (batch element, slice of its kv heads with the query heads that read them);
+        # every piece is one contiguous block of each tensor
+        hkv = self.k.shape[1]
+        per = max(1, hkv // max(1, min(self.e2e_chunks, hkv)))
+        self.e2e_pieces = [(b, h0, min(hkv, h0 + per)) for b in range(self.q.shape[0]) for h0 in range(0, hkv, per)]
+        self.e2e_streams = [torch.cuda.Stream() for _ in range(min(8, len(self.e2e_pieces)))]
+
+    e2e_chunks = 2  # kv-head slices per batch element in the host-copy pipeline
 
     def e2e_step(self):
-        # one stream per batch element: the upload of prompt b + 1 overlaps the kernel and the download of prompt b
-        # (the two copy directions are separate engines); the launching stream joins all of them at the end, so the
-        # events around the timed region see the whole step
+        # one stream per piece (round-robin): the upload of piece i + 1 overlaps the kernel and the download of
+        # piece i (the two copy directions are separate engines); small pieces keep the last download, which
+        # nothing overlaps, short. The launching stream joins all of them at the end, so the events around the
+        # timed region see the whole step
         torch = self.torch
         cur = torch.cuda.current_stream()
-        for b in range(self.q.shape[0]):
-            side = self.e2e_streams[b]
+        g = self.q.shape[1] // self.k.shape[1]
+        for side in self.e2e_streams:
             side.wait_stream(cur)
+        for i, (b, h0, h1) in enumerate(self.e2e_pieces):
+            side = self.e2e_streams[i % len(self.e2e_streams)]
             with torch.cuda.stream(side):
-                self.q[b:b + 1].copy_(self.hq[b:b + 1], non_blocking=True)
-                self.k[b:b + 1].copy_(self.hk[b:b + 1], non_blocking=True)
-                self.v[b:b + 1].copy_(self.hv[b:b + 1], non_blocking=True)
-                self.ops.flash_attention(self.q[b:b + 1], self.k[b:b + 1], self.v[b:b + 1], causal=True,
-                                         out=self.out[b:b + 1], stream=side)
-                self.ho[b:b + 1].copy_(self.out[b:b + 1], non_blocking=True)
+                q, o = self.q[b:b + 1, h0 * g:h1 * g], self.out[b:b + 1, h0 * g:h1 * g]
+                k, v = self.k[b:b + 1, h0:h1], self.v[b:b + 1, h0:h1]
+                q.copy_(self.hq[b:b + 1, h0 * g:h1 * g], non_blocking=True)
+                k.copy_(self.hk[b:b + 1, h0:h1], non_blocking=True)
+                v.copy_(self.hv[b:b + 1, h0:h1], non_blocking=True)
+                self.ops.flash_attention(q, k, v, causal=True, out=o, stream=side)
+                self.ho[b:b + 1, h0 * g:h1 * g].copy_(o, non_blocking=True)
         for side in self.e2e_streams:
             cur.wait_stream(side)
 
@@ -827,6 +838,8 @@ def main():
     ap.add_argument("--no-secondary", action="store_true", help="headline only")
     ap.add_argument("--no-cpu", action="store_true", help="skip the timed host-side legs (for runs under a profiler)")
     ap.add_argument("--e2e-steps", type=int, default=0, help="0 = min(steps, 5)")
+    ap.add_argument("--e2e-chunks", type=int, default=2,
+                    help="prefill host-copy leg: kv-head slices per batch element that travel as separate pieces")
     ap.add_argument("--seed", type=int, default=0)
     ap.add_argument("--dtype", default="bf16", choices=["bf16", "fp16"], help="--workload flash only")
     ap.add_argument("--head-dim", type=int, default=128, choices=[64, 128, 256], help="--workload flash only")
@@ -858,6 +871,7 @@ def main():
     ctx = {"torch": torch, "dist": dist, "device": device, "rank": rank, "world": world, "local_rank": local_rank,
            "threads": threads}
 
+    FlashWorkload.e2e_chunks = max(1, args.e2e_chunks)
     primary_factory, secondary_factories = build_workloads(args, world)
     primary = primary_factory()
     repeats = 1 if args.capture else max(1, args.repeats)
