@@ -812,11 +812,16 @@ def measure(wl, args, steps, repeats, ctx, with_cpu):
             "workload": wl.name, "metric": wl.metric, "value": value, "unit": wl.unit, "n_gpus": world, "steps": steps,
             "warmup": args.warmup, "ms_per_step": step_ms["median"], "scaling": wl.scaling,
             "repeats": {"n": repeats, "value_min": rate(step_ms["max"]), "value_median": value, "value_max": rate(step_ms["min"]),
-                        "ms_min": step_ms["min"], "ms_median": step_ms["median"], "ms_max": step_ms["max"]},
+                        "ms_min": step_ms["min"], "ms_median": step_ms["median"], "ms_max": step_ms["max"],
+                        "ms_blocks": [round(ms / steps, 5) for ms in block_ms]},
             "dtype": wl.dtype_name, "config": wl.config(),
             "roofline": {"bound": wl.bound, "achieved": per_gpu, "peak": peak, "unit": wl.unit,
                          "frac": per_gpu / peak, "peak_source": peaks["source"],
                          "frac_of_nominal": per_gpu / nominal, "traffic": wl.traffic(),
+                         # the median block of a tensor-bound entry runs after the power cap has engaged (see
+                         # repeats.ms_blocks): the library GEMM's figure for that state is given beside the burst one
+                         **({"peak_sustained": peaks["tflops_sustained"], "frac_of_sustained": per_gpu / peaks["tflops_sustained"],
+                             "frac_best_block": rate(step_ms["min"]) / world / peak} if wl.bound == "tensor" else {}),
                          "traffic_unit": "bytes per launch of the dominant kernel (ncu capture, scaled; see profiles/)"},
             "cpu_baseline": cpu, "e2e": e2e,
             "gpu_launches": wl.launches_per_step * steps * repeats,
