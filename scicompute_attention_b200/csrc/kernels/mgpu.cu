@@ -94,7 +94,10 @@ int WaitForCommunicator(NcclApi& api, Communicator* c, int32_t timeout_ms, const
             return Fail(SCA_TIMEOUT, std::string(what) + ": no answer from the other ranks within " + std::to_string(timeout_ms) +
                                          " ms; the communicator was aborted");
         }
-        std::this_thread::sleep_for(std::chrono::microseconds(200));
+        // an enqueue on a non-blocking communicator finishes within microseconds: probe without sleeping first, so
+        // that a decode step does not pay a timer tick, and back off only when the wait is a real one
+        if (Clock::now() - start < std::chrono::microseconds(500)) std::this_thread::yield();
+        else std::this_thread::sleep_for(std::chrono::microseconds(100));
     }
 }
 
