@@ -4,6 +4,7 @@
 // Stands in for src/runtime/launcher.cu:26-111 (smem attribute cache, immediate launch check,
 // SCI_ATTENTION_DEBUG_SYNC) and src/runtime/device_probe.cu:35-84 (the reference's own C ABI).
 #include <cstdlib>
+#include <chrono>
 #include <cstring>
 #include <mutex>
 #include <unordered_map>
@@ -96,6 +97,21 @@ using namespace sca_b200;
 
 extern "C" const char* sca_last_error(void) { return g_last_error.c_str(); }
 
+namespace {
+// The reference's host layer asks the probe on every attention call (DeviceCapability::CudaAvailable,
+// src/runtime/capability.cpp:86-89, called from every backend's Supports / Forward), and cudaGetDeviceProperties
+// alone takes milliseconds. The static part of the answer is therefore kept per device after the first successful
+// probe; the free-memory figure is refreshed when it is older than 50 ms.
+constexpr int kMaxProbedDevices = 64;
+struct CachedProbe {
+    bool valid = false;
+    ScaDeviceProbe probe{};
+    std::chrono::steady_clock::time_point memory_read{};
+};
+std::mutex g_probe_mutex;
+CachedProbe g_probe_cache[kMaxProbedDevices];
+}  // namespace
+
 extern "C" int sca_probe_device(int device_id, ScaDeviceProbe* out) {
     if (out == nullptr) return 1;
     std::memset(out, 0, sizeof(*out));
@@ -108,29 +124,50 @@ extern "C" int sca_probe_device(int device_id, ScaDeviceProbe* out) {
         std::strncpy(out->name, "cuda-unavailable", SCA_DEVICE_NAME_MAX - 1);
         return err != cudaSuccess ? static_cast<int>(err) : 1;
     }
-    cudaDeviceProp prop{};
-    err = cudaGetDeviceProperties(&prop, device_id);
-    if (err != cudaSuccess) {
-        cudaGetLastError();
-        return static_cast<int>(err);
+    const bool cacheable = device_id < kMaxProbedDevices;
+    std::unique_lock<std::mutex> lock(g_probe_mutex, std::defer_lock);
+    if (cacheable) lock.lock();
+    CachedProbe local;
+    CachedProbe& slot = cacheable ? g_probe_cache[device_id] : local;
+    if (!slot.valid) {
+        cudaDeviceProp prop{};
+        err = cudaGetDeviceProperties(&prop, device_id);
+        if (err != cudaSuccess) {
+            cudaGetLastError();
+            return static_cast<int>(err);
+        }
+        ScaDeviceProbe& p = slot.probe;
+        std::memset(&p, 0, sizeof(p));
+        p.binary_has_sm80 = 1;
+        p.binary_has_sm90 = 1;
+        std::strncpy(p.name, prop.name, SCA_DEVICE_NAME_MAX - 1);
+        p.major = prop.major;
+        p.minor = prop.minor;
+        p.sm_count = prop.multiProcessorCount;
+        p.smem_per_sm = prop.sharedMemPerMultiprocessor;
+        p.smem_per_block_default = prop.sharedMemPerBlock;
+        p.smem_per_block_optin = prop.sharedMemPerBlockOptin;
+        p.regs_per_sm = static_cast<unsigned long long>(prop.regsPerMultiprocessor);
+        p.max_threads_per_sm = static_cast<unsigned long long>(prop.maxThreadsPerMultiProcessor);
+        p.l2_bytes = static_cast<unsigned long long>(prop.l2CacheSize);
+        p.total_mem_bytes = prop.totalGlobalMem;
+        p.cuda_available = 1;
+        slot.valid = true;
+        slot.memory_read = {};
     }
-    std::strncpy(out->name, prop.name, SCA_DEVICE_NAME_MAX - 1);
-    out->major = prop.major;
-    out->minor = prop.minor;
-    out->sm_count = prop.multiProcessorCount;
-    out->smem_per_sm = prop.sharedMemPerMultiprocessor;
-    out->smem_per_block_default = prop.sharedMemPerBlock;
-    out->smem_per_block_optin = prop.sharedMemPerBlockOptin;
-    out->regs_per_sm = static_cast<unsigned long long>(prop.regsPerMultiprocessor);
-    out->max_threads_per_sm = static_cast<unsigned long long>(prop.maxThreadsPerMultiProcessor);
-    out->l2_bytes = static_cast<unsigned long long>(prop.l2CacheSize);
-    out->total_mem_bytes = prop.totalGlobalMem;
+    const auto now = std::chrono::steady_clock::now();
     int current = 0;
-    if (cudaGetDevice(&current) == cudaSuccess && current == device_id) {
+    if (now - slot.memory_read > std::chrono::milliseconds(50) && cudaGetDevice(&current) == cudaSuccess &&
+        current == device_id) {
         size_t free_b = 0, total_b = 0;
-        if (cudaMemGetInfo(&free_b, &total_b) == cudaSuccess) out->free_mem_bytes = free_b;
+        if (cudaMemGetInfo(&free_b, &total_b) == cudaSuccess) {
+            slot.probe.free_mem_bytes = free_b;
+            slot.memory_read = now;
+        } else {
+            cudaGetLastError();
+        }
     }
-    out->cuda_available = 1;
+    *out = slot.probe;
     return 0;
 }
 

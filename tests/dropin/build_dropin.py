@@ -11,6 +11,10 @@ the source tree like the other built files):
                functions forwarded to libsca_b200.so): the inner seam - the reference keeps its own dispatcher,
                backends and KV cache and only swaps its CUDA translation units for the C ABI.
 
+The reference's own callers - examples/example_attention.cpp, examples/rollout_engine_stub.cpp and the benchmark
+harness benchmarks/benchmark_attention.cu (both families), benchmarks/benchmark_naive.cu (ref family only: it calls
+the naive launch functions below the public API) - are built the same way, unmodified, as api_<name> / ref_<name>.
+
 Both use tests/dropin/gtest/gtest.h in place of GoogleTest. The reference checkout is found through the
 SCA_REFERENCE_ROOT environment variable (or a `reference` directory beside the repository); without one the
 build is skipped and the tests that need the executables skip as well, unless the executables are already there.
@@ -53,6 +57,15 @@ REF_TESTS = [
 ]
 
 
+# the reference's callers outside its test tree: (path below the reference root, families)
+REF_CALLERS = [
+    ("examples/example_attention.cpp", ("api", "ref")),
+    ("examples/rollout_engine_stub.cpp", ("api", "ref")),
+    ("benchmarks/benchmark_attention.cu", ("api", "ref")),
+    ("benchmarks/benchmark_naive.cu", ("ref",)),
+]
+
+
 def reference_root() -> str | None:
     for cand in (os.environ.get("SCA_REFERENCE_ROOT"), os.path.join(os.path.dirname(ROOT), "reference")):
         if cand and os.path.isdir(os.path.join(cand, "src")) and os.path.isdir(os.path.join(cand, "tests")):
@@ -69,6 +82,9 @@ def executables() -> dict[str, str]:
     out = {}
     for rel in REF_TESTS:
         for family in ("api", "ref"):
+            out[f"{family}_{test_name(rel)}"] = os.path.join(OUT, f"{family}_{test_name(rel)}")
+    for rel, families in REF_CALLERS:
+        for family in families:
             out[f"{family}_{test_name(rel)}"] = os.path.join(OUT, f"{family}_{test_name(rel)}")
     return out
 
@@ -146,6 +162,24 @@ def build(force: bool = False, verbose: bool = False) -> bool:
         if force or _stale(ref_exe, [src, REFHOST_LIB] + headers):
             jobs.append(common + ["-I", os.path.join(ref, "include"), "-I", INFRA] + test_inc +
                         ["-o", ref_exe, "-L", OUT, "-l:libsci_attention_refhost.so", "-L", PKG, "-l:libsca_b200.so"] + rpath)
+    # ---- the reference's examples and benchmark harness ------------------------------------------------------
+    cudart = ["-L", os.path.join(cuda, "lib64"), "-lcudart_static", "-lrt", "-ldl", "-lpthread"]
+    for rel, families in REF_CALLERS:
+        src = os.path.join(ref, rel)
+        name = test_name(rel)
+        caller_inc = ["-I", ref, "-I", os.path.join(ref, "benchmarks"), "-I", os.path.join(ref, "tests"),
+                      "-I", os.path.join(cuda, "include"), f'-DSCA_PROJECT_ROOT="{ref}"', "-x", "c++", src, "-x", "none"]
+        if "api" in families:
+            exe = os.path.join(OUT, "api_" + name)
+            if force or _stale(exe, [src, host_lib] + headers):
+                jobs.append(common + ["-I", INCLUDE, "-I", INFRA] + caller_inc +
+                            ["-o", exe, "-L", PKG, "-l:libsci_attention.so", "-l:libsca_b200.so"] + cudart + rpath)
+        if "ref" in families:
+            exe = os.path.join(OUT, "ref_" + name)
+            if force or _stale(exe, [src, REFHOST_LIB] + headers):
+                jobs.append(common + ["-I", os.path.join(ref, "include"), "-I", os.path.join(ref, "src"), "-I", INFRA] +
+                            caller_inc + ["-o", exe, "-L", OUT, "-l:libsci_attention_refhost.so", "-L", PKG,
+                                          "-l:libsca_b200.so"] + cudart + rpath)
     if jobs:
         with cf.ThreadPoolExecutor(max_workers=8) as pool:
             list(pool.map(_run, jobs))

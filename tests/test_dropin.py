@@ -5,7 +5,9 @@ tests/dropin/build_dropin.py compiles every test file of the reference (tests/un
 reference's headers + the reference's unmodified host layer linked to libsca_b200.so through
 tests/dropin/ref_launch_bindings.cpp (inner seam; that file also carries the static_asserts that pin the C structs
 to the reference PODs). The executables are built where a reference checkout exists and travel with the tree;
-here they are only run.
+here they are only run. The reference's callers outside its test tree - its API example, its rollout example
+and its benchmark harness - are built the same way and run with small arguments: they must finish with exit
+code 0, the harness without a skipped case and without milliseconds of per-call overhead.
 
 Intentional differences, excluded by name below and nowhere else:
   * DispatchTest.DecodeForSingleQueryToken expects the dispatch-table revision string "table=r0"; this library's
@@ -82,3 +84,35 @@ def test_bindings_pin_struct_layouts_against_reference_headers():
 def test_reference_tests_pass_on_the_gpu(built, family, name):
     passed, skipped = run_exe(built[f"{family}_{name}"], family)
     assert passed > 0 and skipped == 0, f"{family}_{name}: passed={passed} skipped={skipped}"
+
+
+# the reference's own callers: (name, arguments, families)
+CALLERS = [
+    ("example_attention", [], ("api", "ref")),
+    ("rollout_engine_stub", ["--n", "4", "--max-new", "8"], ("api", "ref")),
+    ("benchmark_attention", ["--suite", "sanity", "--verify", "--runs", "3", "--warmup", "1"], ("api", "ref")),
+    ("benchmark_naive", ["--suite", "sanity", "--runs", "3", "--warmup", "1"], ("ref",)),
+]
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("name,args,families", CALLERS, ids=[c[0] for c in CALLERS])
+def test_reference_examples_and_benchmark_harness_run_unmodified(built, tmp_path, name, args, families):
+    import json
+    for family in families:
+        cmd = [built[f"{family}_{name}"]] + args
+        record = tmp_path / f"{family}_{name}.json"
+        if name != "example_attention":
+            cmd += ["--json", str(record)]
+        proc = subprocess.run(cmd, capture_output=True, text=True, timeout=1500)
+        assert proc.returncode == 0, f"{family}_{name} rc={proc.returncode}\n{proc.stdout[-3000:]}{proc.stderr[-2000:]}"
+        if name == "benchmark_attention":
+            cases = json.loads(record.read_text())["cases"]
+            skipped = [c["case_id"] for c in cases if c.get("skipped")]
+            assert len(cases) >= 4 and not skipped, f"{family}_{name}: {len(cases)} cases, skipped {skipped}"
+            # the harness times whole API calls: a 512-token prefill takes tens of microseconds on this GPU, so a
+            # millisecond means per-call overhead in the host layer under test (e.g. an uncached device probe)
+            quick = [c["latency_ms"]["p50"] for c in cases if c["impl"] == "flash" and c["params"]["Sq"] == 512]
+            assert quick and max(quick) < 1.0, f"{family}_{name}: 512-token flash calls take {quick} ms"
+        elif name != "example_attention":
+            assert record.exists() and record.stat().st_size > 0
