@@ -133,6 +133,7 @@ public:
     sci::Result<AttentionResult> Forward(const sci::Tensor& q, const sci::Tensor& k, const sci::Tensor& v,
                                          const AttentionConfig& cfg) const override {
         const sci::StreamOrderedScope allocations_on_call_stream(StreamHandle(cfg.stream));
+        const ApiRange nvtx_range("NaiveBackend::Forward");
         const sci::Result<AttentionShape> inferred = InferShape(q, k, v, cfg.layout);
         if (!inferred.ok()) return sci::MakeUnexpected<AttentionResult>(inferred.error());
         const AttentionShape shape = *inferred;
@@ -219,6 +220,7 @@ public:
     sci::Result<AttentionResult> Forward(const sci::Tensor& q, const sci::Tensor& k, const sci::Tensor& v,
                                          const AttentionConfig& cfg) const override {
         const sci::StreamOrderedScope allocations_on_call_stream(StreamHandle(cfg.stream));
+        const ApiRange nvtx_range("TiledBackend::Forward");
         const sci::Result<AttentionShape> inferred = InferShape(q, k, v, cfg.layout);
         if (!inferred.ok()) return sci::MakeUnexpected<AttentionResult>(inferred.error());
         const AttentionShape shape = *inferred;
@@ -334,6 +336,7 @@ public:
     sci::Result<AttentionResult> Forward(const sci::Tensor& q, const sci::Tensor& k, const sci::Tensor& v,
                                          const AttentionConfig& cfg) const override {
         const sci::StreamOrderedScope allocations_on_call_stream(StreamHandle(cfg.stream));
+        const ApiRange nvtx_range("FlashBackend::Forward");
         const sci::Result<AttentionShape> inferred = InferShape(q, k, v, cfg.layout);
         if (!inferred.ok()) return sci::MakeUnexpected<AttentionResult>(inferred.error());
         const AttentionShape shape = *inferred;
@@ -367,6 +370,7 @@ public:
                                                int64_t max_seq_q, int64_t max_seq_kv,
                                                const AttentionConfig& cfg) const override {
         const sci::StreamOrderedScope allocations_on_call_stream(StreamHandle(cfg.stream));
+        const ApiRange nvtx_range("FlashBackend::ForwardVarlen");
         if (cu_q == nullptr || cu_kv == nullptr) {
             return Refuse(AttnStatusCode::kShapeMismatch, "varlen requires host-resident cu_seqlens_q/kv");
         }
@@ -515,6 +519,7 @@ public:
     sci::Result<AttentionResult> Forward(const sci::Tensor& q, const sci::Tensor& k, const sci::Tensor& v,
                                          const AttentionConfig& cfg) const override {
         const sci::StreamOrderedScope allocations_on_call_stream(StreamHandle(cfg.stream));
+        const ApiRange nvtx_range("DecodeBackend::Forward");
         const sci::Result<AttentionShape> inferred = InferShape(q, k, v, cfg.layout);
         if (!inferred.ok()) return sci::MakeUnexpected<AttentionResult>(inferred.error());
         const AttentionShape shape = *inferred;
@@ -590,6 +595,7 @@ public:
 sci::Result<AttentionResult> RunPaged(const sci::Tensor& q, const PagedKVCache& kv, const PagedAttentionParams& params,
                                       const AttentionConfig& cfg) {
     const sci::StreamOrderedScope allocations_on_call_stream(StreamHandle(cfg.stream));
+    const ApiRange nvtx_range("RunPaged");
     if (q.ndims() != 4) {
         return Refuse(AttnStatusCode::kShapeMismatch,
                       "paged_attention expects q=[num_seqs, H_q, seq_q, D]; got ndims=" + std::to_string(q.ndims()));
@@ -803,6 +809,7 @@ sci::Result<AttentionResult> paged_attention(const sci::Tensor& q, const PagedKV
 sci::Result<AttentionResult> paged_prefill(const sci::Tensor& q, const PagedKVCache& kv, int64_t num_seqs,
                                            const int32_t* cu_seqlens_q, int64_t layer, const AttentionConfig& cfg) {
     const sci::StreamOrderedScope allocations_on_call_stream(StreamHandle(cfg.stream));
+    const ApiRange nvtx_range("paged_prefill");
     const KVCacheConfig& kcfg = kv.Storage().Config();
     if (q.ndims() != 3 || cu_seqlens_q == nullptr) {
         return Refuse(AttnStatusCode::kShapeMismatch, "paged_prefill expects q=[total_q, H_q, D] and host cu_seqlens_q");

@@ -64,3 +64,15 @@ inline int64_t PartialElements(int64_t batch, int64_t heads, int64_t splits, int
 
 }  // namespace tables
 }  // namespace sca
+
+namespace sca {
+// NVTX range around one public entry point (domain "sci_attention"): a profiler that is attached sees every API call
+// with its name around the kernels it launches; without one the NVTX stubs return at once.
+class ApiRange {
+public:
+    explicit ApiRange(const char* name);
+    ~ApiRange();
+    ApiRange(const ApiRange&) = delete;
+    ApiRange& operator=(const ApiRange&) = delete;
+};
+}  // namespace sca

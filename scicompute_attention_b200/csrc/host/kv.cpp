@@ -277,6 +277,7 @@ sci::Result<sci::Tensor> KVCache::GatherV(int64_t layer, const int32_t* ids, int
 sci::Result<sci::Tensor> KVCache::GatherInternal(int64_t layer, const int32_t* block_ids, int64_t num_blocks, bool is_key,
                                                  sci::Stream* stream) const {
     const sci::StreamOrderedScope allocations_on_call_stream(StreamHandle(stream));
+    const ApiRange nvtx_range("KVCache::GatherInternal");
     if (layer < 0 || layer >= cfg_.num_layers) {
         return sci::MakeUnexpected<sci::Tensor>(
             MakeStatus(AttnStatusCode::kShapeMismatch, "KVCache::Gather layer=" + std::to_string(layer) + " out of range"));
@@ -364,6 +365,7 @@ sci::Result<PagedKVCache> PagedKVCache::Create(const KVCacheConfig& cfg, sci::De
 sci::Status PagedKVCache::AppendTokens(int64_t seq_id, int64_t layer, const sci::Tensor& k_new, const sci::Tensor& v_new,
                                        sci::Stream* stream) {
     const sci::StreamOrderedScope allocations_on_call_stream(StreamHandle(stream));
+    const ApiRange nvtx_range("PagedKVCache::AppendTokens");
     if (seq_id < 0 || seq_id >= cfg_.max_num_seqs) {
         return MakeStatus(AttnStatusCode::kShapeMismatch, "PagedKVCache::AppendTokens seq_id=" + std::to_string(seq_id) +
                                                               " out of range [0," + std::to_string(cfg_.max_num_seqs) + ")");
@@ -425,6 +427,7 @@ sci::Status PagedKVCache::AppendTokens(int64_t seq_id, int64_t layer, const sci:
 sci::Status PagedKVCache::AppendTokenBatch(int64_t num_seqs, int64_t layer, const sci::Tensor& k_new, const sci::Tensor& v_new,
                                            sci::Stream* stream) {
     const sci::StreamOrderedScope allocations_on_call_stream(StreamHandle(stream));
+    const ApiRange nvtx_range("PagedKVCache::AppendTokenBatch");
     if (num_seqs <= 0 || num_seqs > cfg_.max_num_seqs) {
         return MakeStatus(AttnStatusCode::kShapeMismatch, "PagedKVCache::AppendTokenBatch num_seqs=" + std::to_string(num_seqs) +
                                                               " out of range [1," + std::to_string(cfg_.max_num_seqs) + "]");

@@ -222,3 +222,25 @@ sci::Status Workspace::Reset() {
 }
 
 }  // namespace sca
+
+// ---- NVTX ranges around the public entry points ----------------------------------------------------------
+#include <nvtx3/nvToolsExt.h>
+
+namespace sca {
+namespace {
+nvtxDomainHandle_t ApiDomain() {
+    static nvtxDomainHandle_t domain = nvtxDomainCreateA("sci_attention");
+    return domain;
+}
+}  // namespace
+
+ApiRange::ApiRange(const char* name) {
+    nvtxEventAttributes_t attr{};
+    attr.version = NVTX_VERSION;
+    attr.size = NVTX_EVENT_ATTRIB_STRUCT_SIZE;
+    attr.messageType = NVTX_MESSAGE_TYPE_ASCII;
+    attr.message.ascii = name;
+    nvtxDomainRangePushEx(ApiDomain(), &attr);
+}
+ApiRange::~ApiRange() { nvtxDomainRangePop(ApiDomain()); }
+}  // namespace sca
